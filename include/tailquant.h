@@ -1,0 +1,174 @@
+/* tailquant.h -- C ABI of libtailquant.so: the split W4A4 + tail linear on B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (`cudaStream_t` passed as void*; NULL = the legacy default stream), enqueues its work on
+ * that stream and returns immediately.  Return value: 0 on success, a negative TQ_ERR_*
+ * code otherwise (tq_error_string() gives text, tq_last_cuda_error() the CUDA runtime
+ * message of the last failed launch on the calling thread).  No entry point allocates
+ * device memory: the caller owns every buffer, as in the reference's extensions
+ * ("all pre-allocated, written in place").
+ *
+ * "Reference" citations name files of Smilesky18/tailquant-kernel by their path in that
+ * project.
+ */
+#ifndef TAILQUANT_H_
+#define TAILQUANT_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_OK 0
+#define TQ_ERR_BAD_ARG (-1)       /* null pointer, non-positive size, R >= K, ...             */
+#define TQ_ERR_UNSUPPORTED (-2)   /* K / rotation kind / R outside the compiled set          */
+#define TQ_ERR_MISALIGNED (-3)    /* a pointer that must be 16-byte aligned is not           */
+#define TQ_ERR_CUDA (-4)          /* a CUDA runtime / driver call failed                     */
+#define TQ_ERR_DEVICE_STATUS (-5) /* a bounded device-side wait ran out (see tq_gemm_status) */
+#define TQ_ERR_TOO_LARGE (-6)     /* beyond a stated maximum (no-allocation entry point)     */
+
+/* Rotation applied to the last dimension before quantisation. */
+#define TQ_HAD_NONE 0     /* input is already rotated                                       */
+#define TQ_HAD_WHT 1      /* K = 2^n, 512..8192 : normalised Walsh-Hadamard                 */
+#define TQ_HAD_KRON12 2   /* K = 12*2^n (3072, 12288): (H12 (x) H_2^n)/sqrt(K), H12 = Paley */
+#define TQ_HAD_BLOCK128 3 /* K % 2048 == 0 (e.g. 14336): block-diagonal H128/sqrt(128)      */
+
+/* 16-bit float formats of activation inputs / outputs. */
+#define TQ_BF16 0
+#define TQ_FP16 1
+
+int tq_version(void);
+const char* tq_error_string(int code);
+const char* tq_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Prologue: rotation + per-token INT4 quantisation + top-R tail split, one kernel.
+ *
+ * Replaces, in the reference: the online rotation `RealPolicyLinear._rotate` (call sites
+ * tools/bench_hadamard_three_schemes_quarot_dense_sharedqkv_inplace_fusedtopr_v43.py:482),
+ * the select+pack kernels tools/fused_topr_pack_ext_v55.py:32-151 and
+ * tools/fused_threshold_topr_pack_ext_v57.py:48-269, and for R == 0 the pure per-token
+ * pack `pack_a_full_s4` (call site ...fusedtopr_v43.py:260).
+ *
+ *   x            [M,K] bf16, row-major, 16-byte aligned
+ *   had_kind     TQ_HAD_*
+ *   R            tail entries per row, 0 <= R < K (0 = pure per-token INT4)
+ *   descending_rank  1-based rank (in |x| descending order, ties by lowest index) whose
+ *                magnitude sets the body scale; R+1 = absmax of the body
+ *   a_pack       [M,K/2] u8 : element 2i -> low nibble, 2i+1 -> high nibble; tail positions 0
+ *   body_scale   [M] f32 = max(|x|_(rank), eps) / 7
+ *   top_scale    [M] f32 = max(|x|_max, eps) / 7                     (may be NULL)
+ *   tail_idx16   [M,tail_ld] u16 ascending channel indices, R per row (tail mode T16; may be NULL)
+ *   tail_val     [M,tail_ld] bf16 rotated values at those indices    (T16; may be NULL)
+ *   tail_ld      row pitch (elements) of tail_idx16 / tail_val, >= R; idx32 / top_q are dense [M,R]
+ *   idx32        [M,R] i32 the same indices                          (T4; may be NULL)
+ *   top_q        [M,R] i8  clamp(rint(x / top_scale), -8, 7)         (T4; may be NULL)
+ *   x_rot        [M,K] bf16 rotated activations                      (debug / weight prep; may be NULL)
+ */
+int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank, float eps,
+                      uint8_t* a_pack, float* body_scale, float* top_scale,
+                      uint16_t* tail_idx16, void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q,
+                      void* x_rot, void* stream);
+
+/* Reference-signature select+pack on an already rotated matrix (T4 outputs):
+ * fused_topr_pack(A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps)
+ *   tools/fused_topr_pack_ext_v55.py:112-121
+ * threshold_topr_pack(<same>)
+ *   tools/fused_threshold_topr_pack_ext_v57.py:236-245
+ * Both names map here; indices are written in ascending order. `dtype` is TQ_BF16
+ * (TQ_FP16, the reference's input type, is answered with TQ_ERR_UNSUPPORTED). */
+int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int descending_rank,
+                 uint8_t* A_pack, float* body_scale, float* top_scale, int8_t* top_q, int32_t* idx,
+                 float eps, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Offline weight preparation.  Replaces the external `pack_weight_colmajor_s4` /
+ * `pack_weight_rowmajor_s4_from_scale` (call sites
+ * tools/bench_v61_dense_sparse_matrix_breakdown_v1.py:124-131), the RTN scale
+ * tools/bench_multimodel_all_layers_policy_fastqf_v29.py:245-247 and the offline rotation
+ * tools/bench_real_split_fullstack_rtn_ppl_v1.py:92-110.
+ *
+ *   w        [N,K] bf16 (nn.Linear.weight layout)
+ *   b_col    [N,K/2] u8  INT4 codes, K-contiguous per output channel
+ *   w_scale  [N] f32 = max(amax|w_rot| / 7, eps)
+ *   w_rot    [N,K] bf16 rotated weight (may be NULL when w_t is NULL)
+ *   b_row    [K,N/2] u8  INT4 codes, low nibble = even n          (T4 tail; may be NULL)
+ *   w_t      [K,N] bf16 rotated weight, input-channel major: row k is what a tail entry with
+ *            index k multiplies                                   (T16 tail; may be NULL)
+ */
+int tq_prepare_weight(const void* w, int N, int K, int had_kind, float eps,
+                      uint8_t* b_col, float* w_scale, void* w_rot, uint8_t* b_row, void* w_t,
+                      void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Dense INT4 x INT4 GEMM on tcgen05 (kind::i8, int32 accumulators in tensor memory).
+ * K % 128 == 0; a_pack and b_col 16-byte aligned.
+ *
+ * tq_int4_matmul replaces `qext.matmul(A_pack[M,K/2], B_col[N,K/2]) -> int32 [M,N]`
+ * (call site tools/bench_hadamard_three_schemes_quarot_dense_sharedqkv_inplace_fusedtopr_v43.py:235-239)
+ * and `main_ext.cutlass_s4_gemm` (tools/bench_standalone_int4_vs_torch_gemm_v12.py:149-157).
+ * split_k > 1 splits the reduction over that many CTAs per tile and accumulates with int32
+ * atomics: C must then be zero on entry (the small-M decode path).
+ */
+int tq_int4_matmul(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, int N, int K,
+                   int split_k, void* stream);
+
+/* GEMM with the dequant fused into its epilogue; replaces the reference's GEMM followed by
+ * `scale_i32_to_fp16` (call sites ...fusedtopr_v43.py:262,283) and its fused-epilogue
+ * prototypes tools/quarot_split_fused_epilogue_ext_v1.py:283-432:
+ *   out[m,n] = bf16( (float(acc) * body_scale[m]) * w_scale[n] + tail[m,n] + bias[n] )
+ * `tail` ([M,N] f32, the result of tq_tail_gather) and `bias` ([N] f32) may be NULL. */
+int tq_split_gemm_fused(const uint8_t* a_pack, const float* body_scale, const uint8_t* b_col,
+                        const float* w_scale, const float* tail, const float* bias, void* out_bf16,
+                        int M, int N, int K, void* stream);
+
+/* Finisher of the split-K path: out = bf16((float(C)*body_scale[m])*w_scale[n] + tail + bias). */
+int tq_dequant_finish(const int32_t* C, const float* body_scale, const float* w_scale,
+                      const float* tail, const float* bias, void* out_bf16, int M, int N, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Sparse tail correction, tail mode T16 (bf16 values, 16-bit indices, bf16 weight rows):
+ *   tail[m,n] = sum_r  tail_val[m,r] * w_t[tail_idx16[m,r], n]
+ * evaluated as one fp32 fused-multiply-add chain per output in ascending index order.
+ * Replaces `sparse_top_add_rowmajor_quad_shared` (call sites ...fusedtopr_v43.py:287-295)
+ * and tools/sparse_correction_add_ext_v1.py:64-123 for the bf16-tail mode.
+ * `tail` is [M,N] f32, fully written by this call.  N % 8 == 0, K <= 65536.
+ */
+int tq_tail_gather(const uint16_t* tail_idx16, const void* tail_val, const void* w_t,
+                   float* tail, int M, int N, int K, int R, int tail_ld, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Reference-compatible tail mode T4 (INT4 tail codes against the INT4 weight rows).
+ *
+ * tq_scale_sparse_epilogue: scale_sparse_epilogue_quad|oct(C, body_scale, top_q, idx,
+ *   B_row_pack, top_scale, w_scale, out, K)   tools/fused_sparse_epilogue_ext_v58.py:123-169
+ *   out[m,n] = f16( float(C)*bs[m]*ws[n] + float(sum_r tq*qw[idx,n])*ts[m]*ws[n] )
+ * tq_sparse_correction_add: sparse_correction_add_{bf16,fp16}_oct(out, top_q, idx, B_row_pack,
+ *   top_scale, w_scale)                        tools/sparse_correction_add_ext_v1.py:175-224
+ *   out[m,n] = f16( float(out[m,n]) + float(sum)*ts[m]*ws[n] ),  w_scale f32 or bf16
+ * tq_sparse_top_write: sparse_{i32,u16}_c{4,8,16}_b{128,256}(...) write-only variants
+ *                                              tools/split_sparse_idx16_ext_v1.py:50-109
+ * tq_idx_i32_to_u16: idx_i32_to_u16            tools/split_sparse_idx16_ext_v1.py:31-48
+ * `out_dtype` is TQ_BF16 or TQ_FP16; `idx_u16` selects 16-bit indices. */
+int tq_scale_sparse_epilogue(const int32_t* C, const float* body_scale, const int8_t* top_q,
+                             const int32_t* idx, const uint8_t* b_row, const float* top_scale,
+                             const float* w_scale, void* out, int out_dtype, int M, int N, int K, int R,
+                             void* stream);
+int tq_sparse_correction_add(void* out, int out_dtype, const int8_t* top_q, const int32_t* idx,
+                             const uint8_t* b_row, const float* top_scale, const void* w_scale,
+                             int w_scale_bf16, int M, int N, int K, int R, void* stream);
+int tq_sparse_top_write(void* out, int out_dtype, const int8_t* top_q, const void* idx, int idx_u16,
+                        const uint8_t* b_row, const float* top_scale, const float* w_scale,
+                        int M, int N, int K, int R, void* stream);
+int tq_idx_i32_to_u16(const int32_t* idx, uint16_t* out, long long n, void* stream);
+
+/* Status word of the last GEMM launches on the current device: 0, or a code naming the
+ * pipeline wait that ran out of its iteration budget (the kernel then drains and returns
+ * instead of spinning).  Synchronises the device. */
+int tq_gemm_status(unsigned int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TAILQUANT_H_ */

@@ -1,0 +1,55 @@
+// Shared device helpers for the split W4A4 + tail kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tailquant.h"
+
+namespace tq {
+
+// ---------------------------------------------------------------------------- host side
+void set_last_cuda_error(cudaError_t e);
+int check_launch();  // cudaGetLastError -> TQ_OK / TQ_ERR_CUDA
+
+int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float eps, int scale_mode,
+                 uint8_t* a_pack, float* body_scale, float* top_scale, uint16_t* tail_idx16,
+                 void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q, void* x_rot, cudaStream_t st);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------------------- bf16 bits
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits) { return __uint_as_float(bits << 16); }
+
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+
+// clamp(rint(x / scale), -8, 7) with true fp32 division semantics.  The product with the
+// reciprocal decides every case that is not within 1e-3 of a rounding boundary (its error
+// is below 2e-6 for |t| < 16, and beyond that both evaluations clamp to the same side);
+// the boundary cases take the IEEE division.
+__device__ __forceinline__ int quant_s4(float x, float scale, float rinv) {
+  float t = x * rinv;
+  float r = rintf(t);
+  if (fabsf(fabsf(t - r) - 0.5f) < 1e-3f) r = rintf(__fdiv_rn(x, scale));
+  r = fminf(fmaxf(r, -8.0f), 7.0f);
+  return (int)r;
+}
+
+// ---------------------------------------------------------------------------- vector loads
+__device__ __forceinline__ uint4 ldg_nc_128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+}  // namespace tq

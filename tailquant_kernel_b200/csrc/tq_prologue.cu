@@ -1,0 +1,571 @@
+// Fused prologue of the split W4A4 + tail linear (sm_100a).
+//
+// One CTA of 256 threads works on one row at a time (grid-stride over rows):
+//   1. rotation in fp32 with ascending butterfly strides: radix-16 register passes, the row
+//      travelling between passes through a swizzled fp32 buffer in shared memory;
+//   2. one fp32 multiply by the normalisation and one rounding to bf16;
+//   3. exact rank selection on the 15-bit magnitude keys (distance from the row maximum:
+//      128-wide coarse bins counted in registers, then a 128-bin shared histogram);
+//   4. tail membership with ties broken by lowest index (ballot bitmaps + a prefix over
+//      16-wide groups), tail entries emitted in ascending index order;
+//   5. INT4 codes of the body with true-division semantics, nibble pack, coalesced stores.
+//
+// Reference behaviour covered: tools/fused_threshold_topr_pack_ext_v57.py:96-194 (select,
+// scales, pack), tools/fused_topr_pack_ext_v55.py:21-26,73-109 (clamp_s4, scale = max(key,
+// eps)/7, body nibble 0 at tail positions, nibble order), plus the online rotation that the
+// reference runs as a separate kernel.
+#include <cmath>
+
+#include "tq_common.cuh"
+
+namespace tq {
+namespace {
+
+constexpr int NT = 256;
+constexpr unsigned FULL = 0xffffffffu;
+
+// 12x12 Paley-I Hadamard over GF(11): bit j of row a2 set <=> H[a2][j] = -1.
+__device__ constexpr unsigned short H12_NEG[12] = {0x000, 0x475, 0x8e9, 0x1d3, 0x3a5, 0x749,
+                                                   0xe91, 0xd23, 0xa47, 0x48f, 0x91d, 0x23b};
+
+struct PrologueParams {
+  const __nv_bfloat16* x;
+  int M, R, dr, tail_ld;
+  float eps, hscale;
+  int scale_mode;  // 0: max(t, eps) / 7 (activations); 1: max(t / 7, eps) (weights)
+  uint8_t* a_pack;
+  float* body_scale;
+  float* top_scale;
+  uint16_t* tail_idx16;
+  uint16_t* tail_val;
+  int32_t* idx32;
+  int8_t* top_q;
+  uint16_t* x_rot;
+};
+
+// fp32 word index -> physical word index of the row buffer.  Chosen so that the 128-bit
+// stores of pass 1 and the 32-bit accesses of the later passes are bank-conflict free.
+template <int SWB>
+__device__ __forceinline__ int swz(int i) {
+  return i ^ (((i >> 5) & 3) << 2) ^ (((i >> SWB) & 1) << 4);
+}
+
+template <int N>
+__device__ __forceinline__ void butterflies(float* v) {
+#pragma unroll
+  for (int s = 1; s < N; s <<= 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      if ((i & s) == 0) {
+        float a = v[i], b = v[i + s];
+        v[i] = a + b;
+        v[i + s] = a - b;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& a, float* v) {
+  v[0] = __uint_as_float(a.x << 16);
+  v[1] = __uint_as_float(a.x & 0xffff0000u);
+  v[2] = __uint_as_float(a.y << 16);
+  v[3] = __uint_as_float(a.y & 0xffff0000u);
+  v[4] = __uint_as_float(a.z << 16);
+  v[5] = __uint_as_float(a.z & 0xffff0000u);
+  v[6] = __uint_as_float(a.w << 16);
+  v[7] = __uint_as_float(a.w & 0xffff0000u);
+}
+
+__device__ __forceinline__ uint32_t block_max(uint32_t v, uint32_t* red, int tid) {
+  v = __reduce_max_sync(FULL, v);
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  uint32_t r = red[0];
+#pragma unroll
+  for (int w = 1; w < NT / 32; ++w) r = max(r, red[w]);
+  __syncthreads();
+  return r;
+}
+
+struct SelRes {
+  int kp;       // distance from the row maximum of the key at the requested rank
+  int cnt_lt;   // keys strictly larger (distance strictly smaller)
+  int cnt_eq;   // keys equal to it
+  int next_kp;  // next larger distance present in the same coarse bin, or -1
+};
+
+// rank is 1-based in (key descending) order.  pk[e] holds (bf16 bits << 16) | distance.
+template <int E>
+__device__ __forceinline__ SelRes select_rank(const uint32_t (&pk)[E], int rank, uint32_t* red,
+                                              uint32_t* hist, int* res, int tid) {
+  const int lane = tid & 31, warp = tid >> 5;
+  int below = 0, base = 0, dstar = 0, cum_prev = 0;
+  while (true) {  // uniform across the block: every value below comes from shared memory
+    uint32_t c = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      int dd = (int)((pk[e] & 0xffffu) >> 7) - base;
+      if (dd >= 0 && dd < 4) c += 0x01010101u << (dd * 8);
+    }
+    uint32_t lo = __reduce_add_sync(FULL, c & 0x00ff00ffu);
+    uint32_t hi = __reduce_add_sync(FULL, (c >> 8) & 0x00ff00ffu);
+    if (lane == 0) {
+      red[warp * 2] = lo;
+      red[warp * 2 + 1] = hi;
+    }
+    __syncthreads();
+    lo = 0;
+    hi = 0;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) {
+      lo += red[w * 2];
+      hi += red[w * 2 + 1];
+    }
+    __syncthreads();
+    int cum[4] = {below + (int)(lo & 0xffffu), below + (int)(hi & 0xffffu), below + (int)(lo >> 16),
+                  below + (int)(hi >> 16)};
+    bool found = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (!found && cum[j] >= rank) {
+        found = true;
+        dstar = base + j;
+        cum_prev = j ? cum[j - 1] : below;
+      }
+    }
+    if (found || base >= 256) break;
+    below = cum[3];
+    base += 4;
+  }
+
+  if (tid < 128) hist[tid] = 0;
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    uint32_t kp = pk[e] & 0xffffu;
+    if ((int)(kp >> 7) == dstar) atomicAdd(&hist[kp & 127u], 1u);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = hist[lane * 4 + j];
+    uint32_t s = h[0] + h[1] + h[2] + h[3];
+    uint32_t incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t t = __shfl_up_sync(FULL, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const uint32_t r2 = (uint32_t)(rank - cum_prev);
+    unsigned hit = __ballot_sync(FULL, incl >= r2);
+    unsigned nonempty = __ballot_sync(FULL, s > 0);
+    int fl = hit ? (__ffs(hit) - 1) : 31;
+    if (lane == 0) {
+      res[3] = -1;
+      res[4] = -1;
+    }
+    __syncwarp();
+    if (lane == fl) {
+      uint32_t acc = incl - s;
+      int f = 3;
+#pragma unroll
+      for (int j = 3; j >= 0; --j) {  // smallest j whose running sum reaches r2
+        uint32_t upto = acc;
+#pragma unroll
+        for (int i = 0; i <= j; ++i) upto += h[i];
+        if (upto >= r2) f = j;
+      }
+      uint32_t lt = acc;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (i < f) lt += h[i];
+      res[0] = lane * 4 + f;
+      res[1] = (int)lt;
+      res[2] = (int)h[f];
+      int nx = -1;
+#pragma unroll
+      for (int i = 3; i >= 0; --i)
+        if (i > f && h[i] > 0) nx = lane * 4 + i;
+      res[3] = nx;
+    }
+    unsigned later = (fl < 31) ? (nonempty & ~((2u << fl) - 1u)) : 0u;
+    if (later && lane == __ffs(later) - 1) {
+      int nx = -1;
+#pragma unroll
+      for (int i = 3; i >= 0; --i)
+        if (h[i] > 0) nx = lane * 4 + i;
+      res[4] = nx;
+    }
+  }
+  __syncthreads();
+  SelRes out;
+  out.kp = dstar * 128 + res[0];
+  out.cnt_lt = cum_prev + res[1];
+  out.cnt_eq = res[2];
+  int nb = res[3] >= 0 ? res[3] : res[4];
+  out.next_kp = nb >= 0 ? dstar * 128 + nb : -1;
+  __syncthreads();
+  return out;
+}
+
+__device__ __forceinline__ float make_scale(float t, float eps, int mode) {
+  return mode == 0 ? __fdiv_rn(fmaxf(t, eps), 7.0f) : fmaxf(__fdiv_rn(t, 7.0f), eps);
+}
+
+// resident CTAs per SM the register budget is tuned for
+constexpr int min_ctas(int K) { return K <= 4096 ? 3 : (K <= 8192 ? 2 : 1); }
+
+template <int KIND, int K>
+__global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const PrologueParams p) {
+  constexpr bool BLOCK = (KIND == TQ_HAD_BLOCK128);
+  constexpr int SWB = BLOCK ? 7 : 8;
+  constexpr int E = K / NT;
+  constexpr int L = (KIND == TQ_HAD_KRON12) ? K / 12 : K;
+  static_assert(K % NT == 0 && K % 32 == 0, "K must be a multiple of 256");
+  static_assert(!BLOCK || K % 2048 == 0, "block-128 rotation needs K % 2048 == 0");
+  static_assert(KIND != TQ_HAD_KRON12 || (L % 256 == 0), "kron12 needs K = 12 * 2^n, n >= 8");
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* buf = reinterpret_cast<float*>(smem_raw);
+  // aliases of buf, valid once the rotation has left it
+  uint8_t* pack_s = smem_raw;
+  uint16_t* bm_gt = reinterpret_cast<uint16_t*>(smem_raw + K / 2);
+  uint16_t* bm_eq = reinterpret_cast<uint16_t*>(smem_raw + K / 2 + K / 8);
+  uint32_t* prefix = reinterpret_cast<uint32_t*>(smem_raw + K / 2 + K / 4);
+  unsigned char* after = smem_raw + (size_t)K * 4;
+  uint32_t* hist = reinterpret_cast<uint32_t*>(after);
+  uint32_t* red = hist + 128;
+  int* res = reinterpret_cast<int*>(red + 32);
+  const int Rpad = (p.R + 7) & ~7;
+  uint16_t* st_idx = reinterpret_cast<uint16_t*>(res + 8);
+  uint16_t* st_val = st_idx + Rpad;
+  int8_t* st_q = reinterpret_cast<int8_t*>(st_val + Rpad);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int R = p.R;
+  const int fbase = BLOCK ? ((tid & 15) + 128 * (tid >> 4)) : tid;  // index = fbase + eoff(e)
+  auto eoff = [](int e) -> int { return BLOCK ? (2048 * (e >> 3) + 16 * (e & 7)) : 256 * e; };
+
+  for (int m = blockIdx.x; m < p.M; m += gridDim.x) {
+    const __nv_bfloat16* xrow = p.x + (size_t)m * K;
+    // ---- pass 1: strides 1,2,4,8 on 16 contiguous elements straight from global memory
+#pragma unroll
+    for (int w0 = 0; w0 < K / 16; w0 += NT) {
+      const int w = w0 + tid;
+      if ((K / 16) % NT == 0 || w < K / 16) {
+        const uint4* src = reinterpret_cast<const uint4*>(xrow + 16 * w);
+        uint4 a = ldg_nc_128(src), b = ldg_nc_128(src + 1);
+        float v[16];
+        unpack8(a, v);
+        unpack8(b, v + 8);
+        if (KIND != TQ_HAD_NONE) butterflies<16>(v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<float4*>(buf + swz<SWB>(16 * w + 4 * j)) =
+              make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      }
+    }
+    __syncthreads();
+    // ---- pass 2: strides 16..128 (full transform and 12 (x) 2^n only)
+    if (KIND == TQ_HAD_WHT || KIND == TQ_HAD_KRON12) {
+#pragma unroll
+      for (int w0 = 0; w0 < K / 16; w0 += NT) {
+        const int w = w0 + tid;
+        if ((K / 16) % NT == 0 || w < K / 16) {
+          const int i0 = (w & 15) + ((w >> 4) << 8);
+          float v[16];
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[q] = buf[swz<SWB>(i0 + 16 * q)];
+          butterflies<16>(v);
+#pragma unroll
+          for (int q = 0; q < 16; ++q) buf[swz<SWB>(i0 + 16 * q)] = v[q];
+        }
+      }
+      __syncthreads();
+    }
+    // ---- final pass, ends in registers
+    float v[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) v[e] = buf[swz<SWB>(fbase + eoff(e))];
+    if (KIND == TQ_HAD_WHT) {
+      butterflies<E>(v);  // strides 256 .. K/2
+    } else if (KIND == TQ_HAD_KRON12) {
+      constexpr int EQ = E / 12;  // elements per 2^n segment held by this thread
+#pragma unroll
+      for (int a = 0; a < 12; ++a) butterflies<EQ>(v + a * EQ);
+#pragma unroll
+      for (int q = 0; q < EQ; ++q) {
+        float c[12], o[12];
+#pragma unroll
+        for (int a = 0; a < 12; ++a) c[a] = v[a * EQ + q];
+#pragma unroll
+        for (int a2 = 0; a2 < 12; ++a2) {
+          float acc = (H12_NEG[a2] & 1) ? -c[0] : c[0];
+#pragma unroll
+          for (int a = 1; a < 12; ++a) acc = ((H12_NEG[a2] >> a) & 1) ? acc - c[a] : acc + c[a];
+          o[a2] = acc;
+        }
+#pragma unroll
+        for (int a = 0; a < 12; ++a) v[a * EQ + q] = o[a];
+      }
+    } else if (BLOCK) {
+#pragma unroll
+      for (int g = 0; g < E / 8; ++g) butterflies<8>(v + g * 8);  // strides 16, 32, 64
+    }
+
+    // ---- normalise, round to bf16, keys
+    uint32_t pk[E];
+    uint32_t kmax = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      uint32_t b = f32_to_bf16_bits(v[e] * p.hscale);
+      pk[e] = b << 16;
+      kmax = max(kmax, b & 0x7fffu);
+    }
+    kmax = block_max(kmax, red, tid);  // also orders every read of buf before its reuse below
+#pragma unroll
+    for (int e = 0; e < E; ++e) pk[e] |= kmax - ((pk[e] >> 16) & 0x7fffu);
+
+    // ---- rank selection
+    int Tkp = -1, cnt_lt = 0, body_kp = 0;
+    if (R > 0) {
+      SelRes s = select_rank<E>(pk, R, red, hist, res, tid);
+      Tkp = s.kp;
+      cnt_lt = s.cnt_lt;
+      if (p.dr > s.cnt_lt && p.dr <= s.cnt_lt + s.cnt_eq) {
+        body_kp = s.kp;
+      } else if (p.dr == s.cnt_lt + s.cnt_eq + 1 && s.next_kp >= 0) {
+        body_kp = s.next_kp;
+      } else {
+        body_kp = select_rank<E>(pk, p.dr, red, hist, res, tid).kp;
+      }
+    } else if (p.dr > 1) {
+      body_kp = select_rank<E>(pk, p.dr, red, hist, res, tid).kp;
+    }
+    const int need = R - cnt_lt;
+    const float tscale = make_scale(bf16_bits_to_f32(kmax), p.eps, p.scale_mode);
+    const float bscale = make_scale(bf16_bits_to_f32(kmax - (uint32_t)body_kp), p.eps, p.scale_mode);
+    const float brinv = __fdiv_rn(1.0f, bscale), trinv = __fdiv_rn(1.0f, tscale);
+
+    // ---- tail bitmaps (16 consecutive indices per half warp) and their prefix
+    if (R > 0) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int kp = (int)(pk[e] & 0xffffu);
+        unsigned bg = __ballot_sync(FULL, kp < Tkp), be = __ballot_sync(FULL, kp == Tkp);
+        if ((lane & 15) == 0) {
+          const int g = (fbase + eoff(e)) >> 4;
+          bm_gt[g] = (uint16_t)(bg >> (lane & 16));
+          bm_eq[g] = (uint16_t)(be >> (lane & 16));
+        }
+      }
+      __syncthreads();
+      constexpr int G = K / 16, GPT = (G + NT - 1) / NT;
+      uint32_t loc[GPT], s = 0;
+#pragma unroll
+      for (int j = 0; j < GPT; ++j) {
+        const int g = tid * GPT + j;
+        loc[j] = (g < G) ? ((uint32_t)__popc(bm_gt[g]) | ((uint32_t)__popc(bm_eq[g]) << 16)) : 0u;
+        s += loc[j];
+      }
+      uint32_t incl = s;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        uint32_t t = __shfl_up_sync(FULL, incl, o);
+        if (lane >= o) incl += t;
+      }
+      if (lane == 31) red[warp] = incl;
+      __syncthreads();
+      uint32_t run = incl - s;
+      for (int w = 0; w < warp; ++w) run += red[w];
+#pragma unroll
+      for (int j = 0; j < GPT; ++j) {
+        const int g = tid * GPT + j;
+        if (g < G) prefix[g] = run;
+        run += loc[j];
+      }
+      __syncthreads();
+    }
+
+    // ---- codes, tail entries
+    constexpr int NW = (E + 7) / 8;
+    uint32_t nw[NW];
+#pragma unroll
+    for (int i = 0; i < NW; ++i) nw[i] = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int kp = (int)(pk[e] & 0xffffu);
+      const uint32_t vb = pk[e] >> 16;
+      const float xv = bf16_bits_to_f32(vb);
+      bool is_tail = false;
+      if (R > 0) {
+        const bool gt = kp < Tkp, eq = kp == Tkp;
+        unsigned bg = __ballot_sync(FULL, gt), be = __ballot_sync(FULL, eq);
+        if (gt || eq) {
+          const int i = fbase + eoff(e);
+          const unsigned belowm = (1u << (lane & 15)) - 1u;
+          const unsigned mg = (bg >> (lane & 16)) & 0xffffu, me = (be >> (lane & 16)) & 0xffffu;
+          const uint32_t pre = prefix[i >> 4];
+          const int ngt = (int)(pre & 0xffffu) + __popc(mg & belowm);
+          const int neq = (int)(pre >> 16) + __popc(me & belowm);
+          is_tail = gt || (neq < need);
+          if (is_tail) {
+            const int pos = ngt + min(neq, need);
+            st_idx[pos] = (uint16_t)i;
+            st_val[pos] = (uint16_t)vb;
+            if (p.top_q) st_q[pos] = (int8_t)quant_s4(xv, tscale, trinv);
+          }
+        }
+      }
+      const uint32_t nib = is_tail ? 0u : ((uint32_t)quant_s4(xv, bscale, brinv) & 0xfu);
+      nw[e >> 3] |= nib << (4 * (e & 7));
+      if (p.x_rot) p.x_rot[(size_t)m * K + fbase + eoff(e)] = (uint16_t)vb;
+    }
+    // nibbles of index pairs (2i, 2i+1) sit in adjacent lanes: exchange and form bytes
+    {
+      const int fb_even = BLOCK ? (((tid & ~1) & 15) + 128 * (tid >> 4)) : (tid & ~1);
+#pragma unroll
+      for (int i = 0; i < NW; ++i) {
+        const uint32_t other = __shfl_xor_sync(FULL, nw[i], 1);
+        const uint32_t we = (lane & 1) ? other : nw[i], wo = (lane & 1) ? nw[i] : other;
+        const uint32_t bytes = (lane & 1) ? (((we >> 4) & 0x0f0f0f0fu) | (wo & 0xf0f0f0f0u))
+                                          : ((we & 0x0f0f0f0fu) | ((wo & 0x0f0f0f0fu) << 4));
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int e = 8 * i + 2 * b + (lane & 1);
+          if (e < E) pack_s[(fb_even + eoff(e)) >> 1] = (uint8_t)(bytes >> (8 * b));
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- coalesced copy-out
+    {
+      uint4* dst = reinterpret_cast<uint4*>(p.a_pack + (size_t)m * (K / 2));
+      const uint4* src = reinterpret_cast<const uint4*>(pack_s);
+      for (int i = tid; i < K / 32; i += NT) dst[i] = src[i];
+      const size_t rb = (size_t)m * R, rl = (size_t)m * p.tail_ld;
+      for (int r = tid; r < R; r += NT) {
+        const uint16_t ix = st_idx[r];
+        if (p.tail_idx16) p.tail_idx16[rl + r] = ix;
+        if (p.tail_val) p.tail_val[rl + r] = st_val[r];
+        if (p.idx32) p.idx32[rb + r] = (int32_t)ix;
+        if (p.top_q) p.top_q[rb + r] = st_q[r];
+      }
+      if (tid == 0) {
+        p.body_scale[m] = bscale;
+        if (p.top_scale) p.top_scale[m] = tscale;
+      }
+    }
+    __syncthreads();  // pack_s / bitmaps alias the rotation buffer of the next row
+  }
+}
+
+template <int KIND, int K>
+int launch(const PrologueParams& p, cudaStream_t st) {
+  auto kern = prologue_kernel<KIND, K>;
+  const int Rpad = (p.R + 7) & ~7;
+  const size_t smem = (size_t)K * 4 + (128 + 32 + 8) * 4 + (size_t)Rpad * 5 + 16;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && !(dev < 64 && configured[dev])) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return TQ_ERR_CUDA;
+    }
+    if (dev < 64) configured[dev] = true;
+  }
+  if (smem > 160 * 1024) return TQ_ERR_UNSUPPORTED;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int per_sm = 1;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem);
+  if (per_sm < 1) per_sm = 1;
+  int grid = sms * per_sm;
+  if (grid > p.M) grid = p.M;
+  kern<<<grid, NT, smem, st>>>(p);
+  return check_launch();
+}
+
+#define TQ_CASE(KIND, KK) \
+  if (kind == KIND && K == KK) return launch<KIND, KK>(p, st);
+
+int dispatch(int kind, int K, const PrologueParams& p, cudaStream_t st) {
+  TQ_CASE(TQ_HAD_WHT, 512)
+  TQ_CASE(TQ_HAD_WHT, 1024)
+  TQ_CASE(TQ_HAD_WHT, 2048)
+  TQ_CASE(TQ_HAD_WHT, 4096)
+  TQ_CASE(TQ_HAD_WHT, 8192)
+  TQ_CASE(TQ_HAD_KRON12, 3072)
+  TQ_CASE(TQ_HAD_KRON12, 12288)
+  TQ_CASE(TQ_HAD_BLOCK128, 2048)
+  TQ_CASE(TQ_HAD_BLOCK128, 14336)
+  TQ_CASE(TQ_HAD_NONE, 512)
+  TQ_CASE(TQ_HAD_NONE, 1024)
+  TQ_CASE(TQ_HAD_NONE, 2048)
+  TQ_CASE(TQ_HAD_NONE, 3072)
+  TQ_CASE(TQ_HAD_NONE, 4096)
+  TQ_CASE(TQ_HAD_NONE, 8192)
+  TQ_CASE(TQ_HAD_NONE, 12288)
+  TQ_CASE(TQ_HAD_NONE, 14336)
+  return TQ_ERR_UNSUPPORTED;
+}
+#undef TQ_CASE
+
+float had_scale(int kind, int K) {
+  if (kind == TQ_HAD_NONE) return 1.0f;
+  const double n = (kind == TQ_HAD_BLOCK128) ? 128.0 : (double)K;
+  return (float)(1.0 / sqrt(n));
+}
+
+}  // namespace
+
+int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float eps, int scale_mode,
+                 uint8_t* a_pack, float* body_scale, float* top_scale, uint16_t* tail_idx16,
+                 void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q, void* x_rot, cudaStream_t st) {
+  if ((tail_idx16 || tail_val) && tail_ld < R) return TQ_ERR_BAD_ARG;
+  if (!x || !a_pack || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
+  if (dr < 1 || dr > K) return TQ_ERR_BAD_ARG;
+  if (!aligned16(x) || !aligned16(a_pack)) return TQ_ERR_MISALIGNED;
+  if (M == 0) return TQ_OK;
+  PrologueParams p;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.M = M;
+  p.R = R;
+  p.dr = dr;
+  p.tail_ld = tail_ld;
+  p.eps = eps;
+  p.hscale = had_scale(had_kind, K);
+  p.scale_mode = scale_mode;
+  p.a_pack = a_pack;
+  p.body_scale = body_scale;
+  p.top_scale = top_scale;
+  p.tail_idx16 = tail_idx16;
+  p.tail_val = reinterpret_cast<uint16_t*>(tail_val);
+  p.idx32 = idx32;
+  p.top_q = top_q;
+  p.x_rot = reinterpret_cast<uint16_t*>(x_rot);
+  return dispatch(had_kind, K, p, st);
+}
+
+}  // namespace tq
+
+extern "C" int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank,
+                                 float eps, uint8_t* a_pack, float* body_scale, float* top_scale,
+                                 uint16_t* tail_idx16, void* tail_val, int tail_ld, int32_t* idx32,
+                                 int8_t* top_q, void* x_rot, void* stream) {
+  return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, body_scale, top_scale,
+                          tail_idx16, tail_val, tail_ld, idx32, top_q, x_rot, (cudaStream_t)stream);
+}
+
+extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int descending_rank,
+                            uint8_t* A_pack, float* body_scale, float* top_scale, int8_t* top_q,
+                            int32_t* idx, float eps, void* stream) {
+  if (dtype != TQ_BF16) return TQ_ERR_UNSUPPORTED;
+  if (R > 0 && (!top_q || !idx || !top_scale)) return TQ_ERR_BAD_ARG;
+  return tq::run_prologue(A, M, K, TQ_HAD_NONE, R, descending_rank, eps, 0, A_pack, body_scale, top_scale,
+                          nullptr, nullptr, 0, idx, top_q, nullptr, (cudaStream_t)stream);
+}

@@ -1,0 +1,122 @@
+"""The split W4A4 + tail linear as a host-side object, and the module-level callable the
+reference's drop-in adapter discovers.
+
+Forward of one linear (mirrors the step list of `RealPolicyLinear.forward` as restated in
+tools/profile_multimodel_split_components_v34.py:93-272):
+    prologue (rotation + select + pack)  ->  tail gather (R > 0)  ->  GEMM with fused dequant,
+    tail add and bias.  Rows M <= `small_m` take the split-K GEMM and a finisher instead.
+Everything runs on the current CUDA stream out of per-(M) workspaces that are allocated once, so
+a forward is capturable in a CUDA graph after its first call, as the reference's benches require
+(tools/bench_hadamard_three_schemes_quarot_dense_sharedqkv_inplace_fusedtopr_v43.py:105-123).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import ops
+
+
+class _Workspace:
+    def __init__(self, M: int, K: int, N: int, R: int, device):
+        ld = (R + 7) // 8 * 8
+        self.pro = ops.PrologueOut(
+            a_pack=torch.empty((M, K // 2), dtype=torch.uint8, device=device),
+            body_scale=torch.empty(M, dtype=torch.float32, device=device),
+            top_scale=torch.empty(M, dtype=torch.float32, device=device),
+            tail_idx=torch.zeros((M, ld), dtype=torch.int16, device=device) if R else None,
+            tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=device) if R else None,
+            R=R)
+        self.tail = torch.empty((M, N), dtype=torch.float32, device=device) if R else None
+        self.acc = None  # int32 [M, N], split-K path only
+        self.out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+
+
+class SplitLinear:
+    """Prepared weights + workspaces of one linear layer y = x W^T (+ bias)."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, ratio: float = 0.05,
+                 activation_percentile: float = 100.0, had_kind: Optional[int] = None, small_m: int = 64,
+                 split_k: int = 0):
+        if not weight.is_cuda:
+            raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
+        self.N, self.K = int(weight.shape[0]), int(weight.shape[1])
+        self.ratio = float(ratio)
+        self.R = ops.ceil_ratio_count(self.K, self.ratio)
+        _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
+        self.w = ops.prepare_weight(weight, had_kind, t16=self.R > 0, bias=bias)
+        self.small_m = int(small_m)
+        self.split_k = int(split_k)
+        self._ws: Dict[int, _Workspace] = {}
+
+    def workspace(self, M: int) -> _Workspace:
+        ws = self._ws.get(M)
+        if ws is None:
+            ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device)
+        return ws
+
+    def _pick_split_k(self, M: int) -> int:
+        if self.split_k > 0:
+            return self.split_k
+        tiles = ((M + 127) // 128) * ((self.N + 127) // 128)
+        kb = self.K // 128
+        s = max(1, min(kb, (148 + tiles - 1) // tiles))
+        return s
+
+    def prologue(self, x2d: torch.Tensor) -> _Workspace:
+        ws = self.workspace(x2d.shape[0])
+        ops.split_prologue(x2d, self.w.had_kind, self.R, self.descending_rank, out=ws.pro)
+        return ws
+
+    def compute(self, ws: _Workspace, M: int) -> torch.Tensor:
+        """GEMM + tail for a workspace whose prologue outputs are filled (shared-prologue use:
+        several linears with the same K, R and rank may run `compute` on one prologue, the way the
+        reference shares one prepare between q/k/v and gate/up:
+        tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:124-134)."""
+        w, pro = self.w, ws.pro
+        if self.R:
+            ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
+        if M <= self.small_m:
+            if ws.acc is None:
+                ws.acc = torch.empty((M, self.N), dtype=torch.int32, device=ws.out.device)
+            ops.matmul_splitk(pro.a_pack, w.b_col, ws.acc, self._pick_split_k(M))
+            ops.dequant_finish(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
+        else:
+            ops.split_gemm_fused(pro.a_pack, pro.body_scale, w.b_col, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
+        return ws.out
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2d = x.reshape(-1, self.K)
+        if x2d.dtype != torch.bfloat16:
+            x2d = x2d.to(torch.bfloat16)
+        x2d = x2d.contiguous()
+        M = x2d.shape[0]
+        ws = self.prologue(x2d)
+        y = self.compute(ws, M)
+        return y.view(*lead, self.N)
+
+    __call__ = forward
+
+
+_CACHE: Dict[Tuple, SplitLinear] = {}
+
+
+def split_linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                         ratio: float = 0.05, split_ratio: Optional[float] = None) -> torch.Tensor:
+    """Callable the reference's adapter binds (tools/split_backend_adapter_v1.py:92-116): called as
+    fn(x [M,K], weight [N,K], bias=, ratio=) on every forward with the RAW weight, so prepared weights
+    are cached per (storage, version, shape, ratio).  Returns [M, N] in x's dtype.  The returned
+    tensor is a per-layer workspace that the next call of the same layer overwrites."""
+    if split_ratio is not None:
+        ratio = split_ratio
+    if weight.dim() != 2 or x.shape[-1] != weight.shape[1]:
+        raise RuntimeError(f"weight must be [N, K] with K = x.shape[-1]; got {tuple(weight.shape)} for x {tuple(x.shape)}")
+    key = (weight.data_ptr(), weight._version, tuple(weight.shape), float(ratio),
+           None if bias is None else (bias.data_ptr(), bias._version))
+    lin = _CACHE.get(key)
+    if lin is None:
+        lin = _CACHE[key] = SplitLinear(weight, bias, ratio)
+    y = lin.forward(x)
+    return y if y.dtype == x.dtype else y.to(x.dtype)

@@ -1,0 +1,434 @@
+"""Operator layer: the reference's extension entry points, backed by libtailquant.so.
+
+Names, argument order, in-place convention ("caller allocates, kernel writes on the current
+CUDA stream") and error behaviour (RuntimeError with a message) follow the reference's
+pybind functions:
+
+  fused_topr_pack / threshold_topr_pack ........ tools/fused_topr_pack_ext_v55.py:112-155,
+                                                 tools/fused_threshold_topr_pack_ext_v57.py:236-273
+  scale_sparse_epilogue_quad / _oct ............. tools/fused_sparse_epilogue_ext_v58.py:123-174
+  sparse_correction_add_{bf16,fp16}_oct ......... tools/sparse_correction_add_ext_v1.py:175-224
+  sparse_{i32,u16}_c{4,8,16}_b{128,256}, idx_i32_to_u16  tools/split_sparse_idx16_ext_v1.py:138-163
+  matmul(A_pack, B_pack) -> int32 ............... call site tools/bench_hadamard_three_schemes_quarot_dense_sharedqkv_inplace_fusedtopr_v43.py:235-239
+
+plus the entry points that only exist here (bf16 tail, fused rotation, fused dequant):
+split_prologue, prepare_weight, tail_gather, split_gemm_fused, matmul_splitk, dequant_finish.
+
+PyTorch is used for device memory and streams only.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import TQ_BF16, TQ_FP16, TQ_HAD_BLOCK128, TQ_HAD_KRON12, TQ_HAD_NONE, TQ_HAD_WHT
+
+EPS = 1e-8
+
+
+# --------------------------------------------------------------------------- helpers
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_cuda(t: torch.Tensor, name: str, dtype=None) -> None:
+    _check(torch.is_tensor(t) and t.is_cuda, f"{name} must be a CUDA tensor")
+    _check(t.is_contiguous(), f"{name} must be contiguous")
+    if dtype is not None:
+        _check(t.dtype == dtype, f"{name} must be {dtype}")
+
+
+def _f16_code(dtype) -> int:
+    if dtype == torch.bfloat16:
+        return TQ_BF16
+    if dtype == torch.float16:
+        return TQ_FP16
+    raise RuntimeError("expected a bf16 or fp16 tensor")
+
+
+def ceil_ratio_count(k: int, ratio: float) -> int:
+    """R for a ratio: min(K-1, max(1, ceil(K*ratio))), 0 for ratio <= 0
+    (tools/bench_v61_dense_sparse_matrix_breakdown_v1.py:81-84)."""
+    if ratio <= 0.0:
+        return 0
+    return min(k - 1, max(1, int(math.ceil(k * ratio))))
+
+
+def split_select_params(K: int, R: int, activation_percentile: float = 100.0):
+    """(R, descending_rank, select_k) (tools/bench_qwen3_l18_split_opts_v57.py:83-93)."""
+    pct = min(max(float(activation_percentile), 0.0), 100.0)
+    body_len = K - R
+    body_kth = min(K, max(1, int(math.ceil(body_len * pct / 100.0))))
+    descending_rank = K - body_kth + 1
+    return R, descending_rank, max(R, descending_rank)
+
+
+def default_had_kind(K: int) -> int:
+    """Rotation used for an input dimension: full transform for powers of two, 12 (x) 2^n when
+    K = 12*2^n, else block-diagonal 128 (the reference falls back to a block transform for
+    dimensions its Hadamard helper does not know: tools/romeorot_blockhad_utils_v1.py:34-64)."""
+    if K & (K - 1) == 0:
+        return TQ_HAD_WHT
+    if K % 12 == 0 and (K // 12) & (K // 12 - 1) == 0:
+        return TQ_HAD_KRON12
+    if K % 2048 == 0:
+        return TQ_HAD_BLOCK128
+    raise RuntimeError(f"no rotation is built for K={K}")
+
+
+# --------------------------------------------------------------------------- prologue
+@dataclass
+class PrologueOut:
+    a_pack: torch.Tensor                 # [M, K/2] u8
+    body_scale: torch.Tensor             # [M] f32
+    top_scale: torch.Tensor              # [M] f32
+    tail_idx: Optional[torch.Tensor]     # [M, ld] int16 storage of u16 indices (first R valid)
+    tail_val: Optional[torch.Tensor]     # [M, ld] bf16
+    R: int
+    idx32: Optional[torch.Tensor] = None  # [M, R] i32   (T4)
+    top_q: Optional[torch.Tensor] = None  # [M, R] i8    (T4)
+    x_rot: Optional[torch.Tensor] = None  # [M, K] bf16
+
+
+def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
+                   eps: float = EPS, t16: bool = True, t4: bool = False, want_x_rot: bool = False,
+                   out: Optional[PrologueOut] = None) -> PrologueOut:
+    """Rotation + per-token INT4 + top-R tail split of x [M,K] bf16 in one kernel."""
+    _check_cuda(x, "x", torch.bfloat16)
+    _check(x.dim() == 2, "x must be [M, K]")
+    M, K = x.shape
+    if descending_rank is None:
+        descending_rank = R + 1
+    if out is None:
+        dev = x.device
+        ld = (R + 7) // 8 * 8
+        out = PrologueOut(
+            a_pack=torch.empty((M, K // 2), dtype=torch.uint8, device=dev),
+            body_scale=torch.empty(M, dtype=torch.float32, device=dev),
+            top_scale=torch.empty(M, dtype=torch.float32, device=dev),
+            tail_idx=torch.zeros((M, ld), dtype=torch.int16, device=dev) if (t16 and R) else None,
+            tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=dev) if (t16 and R) else None,
+            R=R,
+            idx32=torch.empty((M, R), dtype=torch.int32, device=dev) if (t4 and R) else None,
+            top_q=torch.empty((M, R), dtype=torch.int8, device=dev) if (t4 and R) else None,
+            x_rot=torch.empty((M, K), dtype=torch.bfloat16, device=dev) if want_x_rot else None,
+        )
+    ld = out.tail_idx.shape[1] if out.tail_idx is not None else 0
+    rc = _lib.load().tq_split_prologue(
+        _ptr(x), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack), _ptr(out.body_scale),
+        _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld, _ptr(out.idx32), _ptr(out.top_q),
+        _ptr(out.x_rot), _stream())
+    _lib.check(rc, f"split_prologue(M={M}, K={K}, had_kind={had_kind}, R={R})")
+    return out
+
+
+def _topr_pack(name, A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps):
+    _check_cuda(A, "A")
+    _check(A.dim() == 2, "A must be [M, K]")
+    _check(A.dtype in (torch.bfloat16, torch.float16), "A must be bf16 (fp16 is not built)")
+    M, K = A.shape
+    R, descending_rank = int(R), int(descending_rank)
+    _check_cuda(A_pack, "A_pack", torch.uint8)
+    _check(A_pack.numel() >= (M * K + 1) // 2, "A_pack is too small")
+    _check_cuda(body_scale, "body_scale", torch.float32)
+    _check_cuda(top_scale, "top_scale", torch.float32)
+    _check(body_scale.numel() >= M and top_scale.numel() >= M, "scale tensors must hold M values")
+    if R > 0:
+        _check_cuda(top_q, "top_q", torch.int8)
+        _check_cuda(idx, "idx", torch.int32)
+        _check(top_q.numel() >= M * R and idx.numel() >= M * R, "top_q / idx must be [M, R]")
+    rc = _lib.load().tq_topr_pack(_ptr(A), _f16_code(A.dtype), M, K, R, descending_rank, _ptr(A_pack),
+                                  _ptr(body_scale), _ptr(top_scale), _ptr(top_q) if R else None,
+                                  _ptr(idx) if R else None, float(eps), _stream())
+    _lib.check(rc, f"{name}(M={M}, K={K}, R={R}, descending_rank={descending_rank})")
+
+
+def fused_topr_pack(A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps) -> None:
+    """tools/fused_topr_pack_ext_v55.py:112-121 (same argument order; idx ascending)."""
+    _topr_pack("fused_topr_pack", A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps)
+
+
+def threshold_topr_pack(A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps) -> None:
+    """tools/fused_threshold_topr_pack_ext_v57.py:236-245 (same argument order)."""
+    _topr_pack("threshold_topr_pack", A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps)
+
+
+# --------------------------------------------------------------------------- weights
+@dataclass
+class PreparedWeight:
+    N: int
+    K: int
+    had_kind: int
+    b_col: torch.Tensor               # [N, K/2] u8
+    w_scale: torch.Tensor             # [N] f32
+    w_t: Optional[torch.Tensor]       # [K, N] bf16   (T16 tail)
+    b_row: Optional[torch.Tensor]     # [K, N/2] u8   (T4 tail)
+    w_rot: Optional[torch.Tensor]     # [N, K] bf16
+    bias: Optional[torch.Tensor] = None  # [N] f32
+
+
+def prepare_weight(W: torch.Tensor, had_kind: Optional[int] = None, eps: float = EPS, t16: bool = True,
+                   t4: bool = False, keep_w_rot: bool = False, bias: Optional[torch.Tensor] = None) -> PreparedWeight:
+    """Offline: rotate the input dim, RTN INT4 per output channel, tail layouts. W is [N,K]."""
+    _check(torch.is_tensor(W) and W.is_cuda and W.dim() == 2, "W must be a CUDA [N, K] tensor")
+    Wb = W.detach().to(torch.bfloat16).contiguous()
+    N, K = Wb.shape
+    if had_kind is None:
+        had_kind = default_had_kind(K)
+    dev = Wb.device
+    b_col = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+    w_scale = torch.empty(N, dtype=torch.float32, device=dev)
+    need_rot = t16 or keep_w_rot
+    w_rot = torch.empty((N, K), dtype=torch.bfloat16, device=dev) if need_rot else None
+    w_t = torch.empty((K, N), dtype=torch.bfloat16, device=dev) if t16 else None
+    b_row = torch.empty((K, N // 2), dtype=torch.uint8, device=dev) if t4 else None
+    rc = _lib.load().tq_prepare_weight(_ptr(Wb), N, K, had_kind, eps, _ptr(b_col), _ptr(w_scale), _ptr(w_rot),
+                                       _ptr(b_row), _ptr(w_t), _stream())
+    _lib.check(rc, f"prepare_weight(N={N}, K={K}, had_kind={had_kind})")
+    b32 = None if bias is None else bias.detach().to(device=dev, dtype=torch.float32).contiguous()
+    return PreparedWeight(N, K, had_kind, b_col, w_scale, w_t, b_row, w_rot if keep_w_rot else None, b32)
+
+
+# --------------------------------------------------------------------------- GEMM
+def _gemm_dims(A_pack, B_pack, M, N, K):
+    _check_cuda(A_pack, "A_pack", torch.uint8)
+    _check_cuda(B_pack, "B_pack", torch.uint8)
+    if M is None:
+        _check(A_pack.dim() == 2 and B_pack.dim() == 2, "A_pack / B_pack must be [M, K/2] / [N, K/2]")
+        M, N, K = A_pack.shape[0], B_pack.shape[0], A_pack.shape[1] * 2
+        _check(B_pack.shape[1] * 2 == K, "A_pack and B_pack disagree on K")
+    _check(A_pack.numel() >= M * K // 2 and B_pack.numel() >= N * K // 2, "packed operand too small")
+    return int(M), int(N), int(K)
+
+
+def matmul(A_pack: torch.Tensor, B_pack: torch.Tensor, M: Optional[int] = None, N: Optional[int] = None,
+           K: Optional[int] = None) -> torch.Tensor:
+    """INT4 x INT4 -> int32 [M,N]; accepts matmul(A, B) and matmul(A, B, M, N, K)
+    (tools/bench_v61_dense_sparse_matrix_breakdown_v1.py:184-187). The only entry point that
+    allocates its result, like the reference's."""
+    M, N, K = _gemm_dims(A_pack, B_pack, M, N, K)
+    C = torch.empty((M, N), dtype=torch.int32, device=A_pack.device)
+    rc = _lib.load().tq_int4_matmul(_ptr(A_pack), _ptr(B_pack), _ptr(C), M, N, K, 1, _stream())
+    _lib.check(rc, f"matmul(M={M}, N={N}, K={K})")
+    return C
+
+
+def matmul_splitk(A_pack, B_pack, C: torch.Tensor, split_k: int, M=None, N=None, K=None) -> torch.Tensor:
+    """Small-M path: the reduction is split over `split_k` CTAs per tile and accumulated with
+    int32 atomics into C, which is zeroed here first."""
+    M, N, K = _gemm_dims(A_pack, B_pack, M, N, K)
+    _check_cuda(C, "C", torch.int32)
+    _check(C.numel() >= M * N, "C too small")
+    C.zero_()
+    rc = _lib.load().tq_int4_matmul(_ptr(A_pack), _ptr(B_pack), _ptr(C), M, N, K, int(split_k), _stream())
+    _lib.check(rc, f"matmul_splitk(M={M}, N={N}, K={K}, split_k={split_k})")
+    return C
+
+
+def split_gemm_fused(A_pack, body_scale, B_pack, w_scale, out, tail=None, bias=None, M=None, N=None, K=None):
+    """out[m,n] = bf16((float(acc)*body_scale[m])*w_scale[n] + tail[m,n] + bias[n])."""
+    M, N, K = _gemm_dims(A_pack, B_pack, M, N, K)
+    _check_cuda(body_scale, "body_scale", torch.float32)
+    _check_cuda(w_scale, "w_scale", torch.float32)
+    _check_cuda(out, "out", torch.bfloat16)
+    _check(out.numel() >= M * N, "out too small")
+    if tail is not None:
+        _check_cuda(tail, "tail", torch.float32)
+        _check(tail.numel() >= M * N, "tail too small")
+    if bias is not None:
+        _check_cuda(bias, "bias", torch.float32)
+    rc = _lib.load().tq_split_gemm_fused(_ptr(A_pack), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale), _ptr(tail),
+                                         _ptr(bias), _ptr(out), M, N, K, _stream())
+    _lib.check(rc, f"split_gemm_fused(M={M}, N={N}, K={K})")
+    return out
+
+
+def dequant_finish(C, body_scale, w_scale, out, tail=None, bias=None):
+    _check_cuda(C, "C", torch.int32)
+    M, N = C.shape
+    _check_cuda(out, "out", torch.bfloat16)
+    rc = _lib.load().tq_dequant_finish(_ptr(C), _ptr(body_scale), _ptr(w_scale), _ptr(tail), _ptr(bias), _ptr(out),
+                                       M, N, _stream())
+    _lib.check(rc, "dequant_finish")
+    return out
+
+
+def tail_gather(tail_idx, tail_val, w_t, tail_out, R: int):
+    """tail_out[m,n] = sum_r tail_val[m,r] * w_t[tail_idx[m,r], n] (fp32 fma chain, ascending r)."""
+    _check_cuda(tail_idx, "tail_idx", torch.int16)
+    _check_cuda(tail_val, "tail_val", torch.bfloat16)
+    _check_cuda(w_t, "w_t", torch.bfloat16)
+    _check_cuda(tail_out, "tail_out", torch.float32)
+    M, ld = tail_idx.shape
+    K, N = w_t.shape
+    _check(tail_val.shape == tail_idx.shape, "tail_idx / tail_val shapes differ")
+    _check(tail_out.numel() >= M * N, "tail_out too small")
+    rc = _lib.load().tq_tail_gather(_ptr(tail_idx), _ptr(tail_val), _ptr(w_t), _ptr(tail_out), M, N, K, int(R), ld,
+                                    _stream())
+    _lib.check(rc, f"tail_gather(M={M}, N={N}, K={K}, R={R})")
+    return tail_out
+
+
+# --------------------------------------------------------------------------- T4 (reference) tail
+def _t4_common(top_q, idx, B_row_pack, top_scale, w_scale, out):
+    _check_cuda(top_q, "top_q", torch.int8)
+    _check_cuda(B_row_pack, "B_row_pack", torch.uint8)
+    _check_cuda(top_scale, "top_scale", torch.float32)
+    _check_cuda(out, "out")
+    _check(top_q.dim() == 2 and out.dim() == 2, "top_q must be [M, R] and out [M, N]")
+    M, R = top_q.shape
+    N = out.shape[1]
+    _check(out.shape[0] == M, "out and top_q disagree on M")
+    _check(idx.numel() == M * R, "idx must be [M, R]")
+    _check(w_scale.numel() >= N and top_scale.numel() >= M, "scale tensors too small")
+    _check((B_row_pack.numel() * 2) % N == 0, "B_row_pack must be [K, N/2]")
+    K = B_row_pack.numel() * 2 // N
+    return M, N, K, R
+
+
+def _scale_sparse_epilogue(name, C, body_scale, top_q, idx, B_row_pack, top_scale, w_scale, out, K):
+    _check_cuda(C, "C", torch.int32)
+    _check_cuda(idx, "idx", torch.int32)
+    _check_cuda(body_scale, "body_scale", torch.float32)
+    _check_cuda(w_scale, "w_scale", torch.float32)
+    M, N, K2, R = _t4_common(top_q, idx, B_row_pack, top_scale, w_scale, out)
+    _check(int(K) == K2, "K does not match B_row_pack")
+    _check(C.numel() == M * N, "C must be [M, N]")
+    rc = _lib.load().tq_scale_sparse_epilogue(_ptr(C), _ptr(body_scale), _ptr(top_q), _ptr(idx), _ptr(B_row_pack),
+                                              _ptr(top_scale), _ptr(w_scale), _ptr(out), _f16_code(out.dtype), M, N,
+                                              K2, R, _stream())
+    _lib.check(rc, name)
+
+
+def scale_sparse_epilogue_quad(C, body_scale, top_q, idx, B_row_pack, top_scale, w_scale, out, K) -> None:
+    """tools/fused_sparse_epilogue_ext_v58.py:123-145 (the column-per-thread count is a tuning
+    detail of the reference; both names run the same kernel here)."""
+    _scale_sparse_epilogue("scale_sparse_epilogue_quad", C, body_scale, top_q, idx, B_row_pack, top_scale, w_scale,
+                           out, K)
+
+
+def scale_sparse_epilogue_oct(C, body_scale, top_q, idx, B_row_pack, top_scale, w_scale, out, K) -> None:
+    """tools/fused_sparse_epilogue_ext_v58.py:147-169."""
+    _scale_sparse_epilogue("scale_sparse_epilogue_oct", C, body_scale, top_q, idx, B_row_pack, top_scale, w_scale,
+                           out, K)
+
+
+def _sparse_correction_add(name, out, top_q, idx, B_row_pack, top_scale, w_scale, out_dtype, ws_dtype):
+    _check_cuda(idx, "idx", torch.int32)
+    _check_cuda(out, "out", out_dtype)
+    _check_cuda(w_scale, "w_scale", ws_dtype)
+    M, N, K, R = _t4_common(top_q, idx, B_row_pack, top_scale, w_scale, out)
+    rc = _lib.load().tq_sparse_correction_add(_ptr(out), _f16_code(out.dtype), _ptr(top_q), _ptr(idx),
+                                              _ptr(B_row_pack), _ptr(top_scale), _ptr(w_scale),
+                                              1 if ws_dtype == torch.bfloat16 else 0, M, N, K, R, _stream())
+    _lib.check(rc, name)
+
+
+def sparse_correction_add_bf16_oct(out, top_q, idx, B_row_pack, top_scale, w_scale) -> None:
+    """tools/sparse_correction_add_ext_v1.py:175-187."""
+    _sparse_correction_add("sparse_correction_add_bf16_oct", out, top_q, idx, B_row_pack, top_scale, w_scale,
+                           torch.bfloat16, torch.float32)
+
+
+def sparse_correction_add_bf16_wscale_bf16_oct(out, top_q, idx, B_row_pack, top_scale, w_scale) -> None:
+    """tools/sparse_correction_add_ext_v1.py:189-201."""
+    _sparse_correction_add("sparse_correction_add_bf16_wscale_bf16_oct", out, top_q, idx, B_row_pack, top_scale,
+                           w_scale, torch.bfloat16, torch.bfloat16)
+
+
+def sparse_correction_add_fp16_oct(out, top_q, idx, B_row_pack, top_scale, w_scale) -> None:
+    """tools/sparse_correction_add_ext_v1.py:203-215."""
+    _sparse_correction_add("sparse_correction_add_fp16_oct", out, top_q, idx, B_row_pack, top_scale, w_scale,
+                           torch.float16, torch.float32)
+
+
+def sparse_top_write(top_q, idx, B_row_pack, top_scale, w_scale, out) -> None:
+    """Write-only sparse term with int32 or uint16 (int16 storage) indices: the eight
+    sparse_{i32,u16}_c{4,8,16}_b{128,256} variants of tools/split_sparse_idx16_ext_v1.py:144-151
+    differ only in launch shape and all map here."""
+    _check(idx.dtype in (torch.int32, torch.int16, torch.uint16), "idx must be int32 or 16-bit")
+    _check_cuda(idx, "idx")
+    _check_cuda(w_scale, "w_scale", torch.float32)
+    M, N, K, R = _t4_common(top_q, idx, B_row_pack, top_scale, w_scale, out)
+    rc = _lib.load().tq_sparse_top_write(_ptr(out), _f16_code(out.dtype), _ptr(top_q), _ptr(idx),
+                                         0 if idx.dtype == torch.int32 else 1, _ptr(B_row_pack), _ptr(top_scale),
+                                         _ptr(w_scale), M, N, K, R, _stream())
+    _lib.check(rc, "sparse_top_write")
+
+
+def idx_i32_to_u16(idx: torch.Tensor, out: torch.Tensor) -> None:
+    """tools/split_sparse_idx16_ext_v1.py:31-48,138-142."""
+    _check_cuda(idx, "idx", torch.int32)
+    _check_cuda(out, "out")
+    _check(out.element_size() == 2 and out.numel() >= idx.numel(), "out must hold idx.numel() 16-bit values")
+    rc = _lib.load().tq_idx_i32_to_u16(_ptr(idx), _ptr(out), idx.numel(), _stream())
+    _lib.check(rc, "idx_i32_to_u16")
+
+
+def gemm_status() -> int:
+    """Device status word of the pipelined kernels (0 = every bounded wait completed)."""
+    import ctypes
+    v = ctypes.c_uint(0)
+    _lib.load().tq_gemm_status(ctypes.byref(v))
+    return int(v.value)
+
+
+# --------------------------------------------------------------------------- loader shims
+class _Ext:
+    """Stands in for the module object the reference's `load_*_ext(verbose=False)` return."""
+
+    def __init__(self, **fns):
+        self.__dict__.update(fns)
+
+
+def load_fused_topr_pack_ext_v55(verbose: bool = False):
+    _lib.load()
+    return _Ext(fused_topr_pack=fused_topr_pack)
+
+
+def load_fused_threshold_topr_pack_ext_v57(verbose: bool = False):
+    _lib.load()
+    return _Ext(threshold_topr_pack=threshold_topr_pack)
+
+
+def load_fused_sparse_epilogue_ext_v58(verbose: bool = False):
+    _lib.load()
+    return _Ext(scale_sparse_epilogue_quad=scale_sparse_epilogue_quad,
+                scale_sparse_epilogue_oct=scale_sparse_epilogue_oct)
+
+
+def load_sparse_correction_add_ext_v1(verbose: bool = False):
+    _lib.load()
+    return _Ext(sparse_correction_add_bf16_oct=sparse_correction_add_bf16_oct,
+                sparse_correction_add_bf16_wscale_bf16_oct=sparse_correction_add_bf16_wscale_bf16_oct,
+                sparse_correction_add_fp16_oct=sparse_correction_add_fp16_oct)
+
+
+def load_split_sparse_idx16_ext_v1(verbose: bool = False):
+    _lib.load()
+    fns = {"idx_i32_to_u16": idx_i32_to_u16}
+    for it in ("i32", "u16"):
+        for c in (4, 8, 16):
+            for b in (128, 256):
+                fns[f"sparse_{it}_c{c}_b{b}"] = sparse_top_write
+    return _Ext(**fns)
+
+
+def load_quarot_sm120_extension_v1(verbose: bool = False):
+    """Name kept from tools/load_quarot_sm120_extension_v1.py; the GEMM behind it is the
+    tcgen05 kernel of this package."""
+    _lib.load()
+    return _Ext(matmul=matmul)

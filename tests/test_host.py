@@ -1,0 +1,166 @@
+"""CPU-side checks: the C ABI library loads and exports what include/tailquant.h declares, the
+policy loader behaves like the reference's, the host helpers agree with the oracle, and the
+multi-rank row sharding is exercised with gloo (world size 2)."""
+import json
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(ROOT, "tests", "golden")
+
+
+def test_library_exports_every_declared_symbol():
+    from tailquant_kernel_b200 import _lib, build
+    build.build()
+    lib = _lib.load()
+    header = open(os.path.join(ROOT, "include", "tailquant.h")).read()
+    declared = set(re.findall(r"^\s*(?:int|const char\*)\s+(tq_\w+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations parsed"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.tq_version() >= 100
+    assert b"aligned" in lib.tq_error_string(-3)
+    assert b"unknown" in lib.tq_error_string(-99)
+
+
+def test_argument_errors_need_no_gpu():
+    import ctypes
+    from tailquant_kernel_b200 import _lib
+    lib = _lib.load()
+    assert lib.tq_split_prologue(None, 1, 4096, 1, 0, 1, 1e-8, None, None, None, None, None, 0, None, None, None, None) == -1
+    assert lib.tq_int4_matmul(None, None, None, 1, 8, 128, 1, None) == -1
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf) & ~15
+    assert lib.tq_int4_matmul(p + 16, p + 16, p + 16, 1, 8, 100, 1, None) == -2   # K % 128
+    assert lib.tq_int4_matmul(p + 17, p + 16, p + 16, 1, 8, 128, 1, None) == -3   # misaligned
+    assert lib.tq_tail_gather(p, p, p, p, 4, 8, 128, 128, 128, None) == -1        # R >= K
+    with pytest.raises(RuntimeError):
+        _lib.check(-2, "x")
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from tailquant_kernel_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libtailquant.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
+
+
+def test_cpu_tensors_are_rejected():
+    import torch
+    from tailquant_kernel_b200 import SplitLinear, ops
+    with pytest.raises(RuntimeError):
+        SplitLinear(torch.zeros(8, 512, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        ops.split_prologue(torch.zeros(2, 512, dtype=torch.bfloat16), 1, 10)
+    with pytest.raises(RuntimeError):
+        ops.matmul(torch.zeros(2, 64, dtype=torch.uint8), torch.zeros(8, 64, dtype=torch.uint8))
+
+
+def test_host_scalars_match_reference_vectors():
+    from tailquant_kernel_b200 import ops
+    for row in json.load(open(os.path.join(GOLD, "scalars.json"))):
+        R = ops.ceil_ratio_count(row["K"], row["ratio"])
+        assert R == row["R"]
+        assert ops.split_select_params(row["K"], R, row["pct"])[1:] == (row["descending_rank"], row["select_k"])
+    assert ops.default_had_kind(4096) == 1 and ops.default_had_kind(12288) == 2 and ops.default_had_kind(14336) == 3
+    with pytest.raises(RuntimeError):
+        ops.default_had_kind(1000)
+
+
+def test_policy_loader_matches_reference_loader():
+    from tailquant_kernel_b200 import policy
+    gold = json.load(open(os.path.join(GOLD, "policy_loader.json")))
+    # a policy in the reference's schema, rebuilt from the loader output recorded in the golden file
+    modules = {}
+    for name, m in gold["sample"].items():
+        modules[name.replace("model.", "", 1)] = {  # "layers.N..." names are normalised to "model.layers.N..."
+            "ratio": gold["raw_first"], "ratio_continuous": m["ratio_continuous"],
+            "ratio_projected": m["ratio_projected"], "activation_percentile": m["activation_percentile"],
+            "weight_percentile": m["weight_percentile"], "history": [1, 2, 3]}
+    with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
+        json.dump({"metadata": {"model": "x"}, "modules": modules}, f)
+    try:
+        got = policy.load_policy(f.name)                      # reference precedence: ratio_projected first
+        assert got["modules"] == gold["sample"]
+        got = policy.load_policy(f.name, prefer="ratio")
+        assert all(m["ratio"] == gold["raw_first"] for m in got["modules"].values())
+        got = policy.load_policy(f.name, force_activation_percentile_100=True)
+        assert all(m["activation_percentile"] == 100.0 for m in got["modules"].values())
+    finally:
+        os.unlink(f.name)
+    pol = policy.make_fixed_ratio_policy(36, 0.05, "Qwen/Qwen3-8B")
+    assert len(pol["modules"]) == gold["n_modules"] == 252
+    e = pol["modules"][policy.policy_key(0, "mlp.down_proj")]
+    assert policy.select_params_for(e, 12288) == (615, 616)
+    assert policy.select_params_for(e, 4096) == (205, 206)
+
+
+def test_row_shard_covers_rows():
+    from tailquant_kernel_b200.shard import all_shards, column_shard, row_shard
+    for M in (0, 1, 7, 2048, 32768, 2049):
+        for w in (1, 2, 4, 8):
+            sh = all_shards(M, w)
+            assert sh[0][0] == 0 and sum(c for _, c in sh) == M
+            assert all(sh[i][0] + sh[i][1] == sh[i + 1][0] for i in range(w - 1))
+            assert max(c for _, c in sh) - min(c for _, c in sh) <= 1
+    assert column_shard(24576, 3, 8) == (9216, 3072)
+    with pytest.raises(ValueError):
+        row_shard(8, 2, 2)
+
+
+_WORKER = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from oracle import oracle as O
+from tailquant_kernel_b200.shard import row_shard
+dist.init_process_group("gloo", rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]))
+rank, world = dist.get_rank(), dist.get_world_size()
+M, K, N, R = 37, 512, 24, 26
+xb = O.make_activations(M, K, seed=0, n_outlier=4)
+w = O.prepare_weight(O.make_weights(N, K, seed=1), O.HAD_WHT)
+s, c = row_shard(M, rank, world)
+y_local = O.split_linear_t16(xb[s:s + c], w, O.HAD_WHT, R)[0].astype(np.int32)
+counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+dist.all_gather(counts, torch.tensor([c]))
+assert sum(int(t) for t in counts) == M
+cmax = max(int(t) for t in counts)
+padded = torch.zeros((cmax, N), dtype=torch.int32)
+padded[:c] = torch.from_numpy(y_local)
+if rank == 0:
+    parts = [torch.zeros((cmax, N), dtype=torch.int32) for _ in counts]
+    dist.gather(padded, parts, dst=0)
+    got = torch.cat([p[:int(t)] for p, t in zip(parts, counts)]).numpy()
+    full = O.split_linear_t16(xb, w, O.HAD_WHT, R)[0].astype(np.int32)
+    assert np.array_equal(got, full), "row-sharded result differs from the unsharded one"
+else:
+    dist.gather(padded, dst=0)
+# the timing rule of the benchmark: max over ranks
+t = torch.tensor([1.0 + rank])
+dist.all_reduce(t, op=dist.ReduceOp.MAX)
+assert float(t) == float(world)
+dist.barrier()
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_two_rank_row_sharding_gloo():
+    with tempfile.NamedTemporaryFile("w", suffix=".py", delete=False) as f:
+        f.write(_WORKER)
+    try:
+        res = subprocess.run(
+            [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+             "--master-addr", "127.0.0.1", "--master-port", "29561", f.name, ROOT],
+            capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    finally:
+        os.unlink(f.name)
