@@ -1,0 +1,369 @@
+#!/usr/bin/env python3
+"""Benchmark of the split W4A4 + tail linear on the Qwen3-8B decoder-layer shapes at prefill.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): the four linears of one Qwen3-8B decoder layer at M = 2048 tokens per GPU and
+tail ratio 0.05 -- qkv_proj 4096->6144 (one fused GEMM), o_proj 4096->4096, gate_up 4096->2x12288 (one
+shared prologue, one GEMM), down_proj 12288->4096 (12 (x) 1024 Hadamard) -- each as prologue + tail
+gather + tcgen05 GEMM with fused dequant.  Synthetic, seeded inputs: activations N(0,1) with 16 channels
+x50, weights N(0, 0.02).  With N GPUs every rank runs the same step on its own 2048 rows (token-row
+sharding, replicated weights, no collective): weak scaling.
+
+The printed JSON line carries the whole-job throughput (`value`, TOPS = 2*M*N*K summed over the four
+linears and all ranks / time), the same metric through the public API with host buffers (`e2e`), the
+roofline of the dense GEMM kernel, the per-kernel breakdown and a CPU baseline (the numpy oracle timed on a
+bounded sample).  `--impl reference` times only that CPU oracle.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYER = [  # name, K, N
+    ("qkv_proj", 4096, 6144),
+    ("o_proj", 4096, 4096),
+    ("gate_up_proj", 4096, 24576),
+    ("down_proj", 12288, 4096),
+]
+M_TOKENS = 2048
+RATIO = 0.05
+CPU_SAMPLE_ROWS = 64
+METRIC = "split W4A4+tail linear TOPS, Qwen3-8B layer shapes, prefill M=2048/GPU, ratio 0.05"
+NOMINAL_INT8_TOPS = 4500.0
+
+
+def layer_ops(m: int) -> float:
+    return float(sum(2.0 * m * n * k for _, k, n in LAYER))
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16": float(d["bf16_tflops"]),
+                "bf16_sustained": float(d["bf16_tflops_sustained"]), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------- CPU oracle arm
+def cpu_oracle_setup():
+    from oracle import oracle as O
+    ws = []
+    for i, (name, K, N) in enumerate(LAYER):
+        kind = O.HAD_KRON12 if K == 12288 else O.HAD_WHT
+        w = O.prepare_weight(O.make_weights(N, K, seed=100 + i), kind)
+        x = O.make_activations(CPU_SAMPLE_ROWS, K, seed=200 + i, n_outlier=16)
+        ws.append((kind, O.ceil_ratio_count(K, RATIO), w, x))
+    return O, ws
+
+
+def cpu_oracle_step(O, ws):
+    for kind, R, w, x in ws:
+        O.split_linear_t16(x, w, kind, R)
+
+
+def cpu_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        n = max([int(p.get("num_threads", 1)) for p in threadpool_info()] or [1])
+        return max(n, 1)
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    O, ws = cpu_oracle_setup()
+    for _ in range(args.warmup):
+        cpu_oracle_step(O, ws)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_step(O, ws)
+    dt = time.perf_counter() - t0
+    ms = dt * 1e3 / max(args.steps, 1)
+    tops = layer_ops(CPU_SAMPLE_ROWS) / (ms * 1e-3) / 1e12
+    sample = (f"numpy restatement of the path (oracle/oracle.py), online part only, all four linears of the layer on "
+              f"{CPU_SAMPLE_ROWS} of the 2048 rows per step")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int4 x int4 -> int32, fp32 dequant, bf16 out",
+        "data": "synthetic",
+        "config": {"workload": "Qwen3-8B decoder layer linears (BASELINE configs[1])", "rows_per_step": CPU_SAMPLE_ROWS,
+                   "tail_ratio": RATIO},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Reads SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._loop, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------- GPU arm
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from tailquant_kernel_b200 import SplitLinear, ops
+    from tailquant_kernel_b200._lib import TQ_HAD_KRON12, TQ_HAD_WHT
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- prepared weights (replicated) and this rank's token rows
+    gen = torch.Generator(device="cpu")
+    lins, xs, host_x, host_y = [], [], [], []
+    for i, (name, K, N) in enumerate(LAYER):
+        gen.manual_seed(100 + i)
+        W = (torch.randn((N, K), generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(dev)
+        lin = SplitLinear(W, ratio=RATIO, had_kind=TQ_HAD_KRON12 if K == 12288 else TQ_HAD_WHT)
+        del W
+        gen.manual_seed(1000 * (rank + 1) + i)
+        x = torch.randn((M_TOKENS, K), generator=gen, dtype=torch.float32)
+        ch = torch.randperm(K, generator=gen)[:16]
+        x[:, ch] *= 50.0
+        hx = x.to(torch.bfloat16).pin_memory()
+        lins.append(lin)
+        host_x.append(hx)
+        xs.append(hx.to(dev))
+        host_y.append(torch.empty((M_TOKENS, N), dtype=torch.bfloat16).pin_memory())
+    dev_x = [torch.empty_like(x) for x in xs]
+    torch.cuda.synchronize()
+
+    def step():
+        for lin, x in zip(lins, xs):
+            lin.forward(x)
+
+    def step_e2e():
+        for lin, hx, dx, hy in zip(lins, host_x, dev_x, host_y):
+            dx.copy_(hx, non_blocking=True)
+            y = lin.forward(dx)
+            hy.copy_(y, non_blocking=True)
+
+    def timed(fn, steps, warmup, sample_clocks=False):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        sampler = ClockSampler(local) if sample_clocks else None
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if sampler else None
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, clocks
+
+    ms_step, clocks = timed(step, args.steps, args.warmup, sample_clocks=True)
+    ms_e2e, _ = timed(step_e2e, args.steps, max(args.warmup, 3))
+    assert ops.gemm_status() == 0, "a bounded device-side wait ran out during the benchmark"
+
+    # ---- per-kernel device time over the same four linears (CUDA events on the launching stream)
+    def kernel_ms(fn, reps=10):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    wss = [lin.workspace(M_TOKENS) for lin in lins]
+
+    def all_prologue():
+        for lin, x, ws in zip(lins, xs, wss):
+            ops.split_prologue(x, lin.w.had_kind, lin.R, lin.descending_rank, out=ws.pro)
+
+    def all_tail():
+        for lin, ws in zip(lins, wss):
+            ops.tail_gather(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R)
+
+    def all_gemm():
+        for lin, ws in zip(lins, wss):
+            ops.split_gemm_fused(ws.pro.a_pack, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out, tail=ws.tail)
+
+    t_pro, t_tail, t_gemm = kernel_ms(all_prologue), kernel_ms(all_tail), kernel_ms(all_gemm)
+    per_linear = {}
+    for (name, K, N), lin, x, ws in zip(LAYER, lins, xs, wss):
+        g = kernel_ms(lambda: ops.split_gemm_fused(ws.pro.a_pack, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out,
+                                                   tail=ws.tail))
+        t = kernel_ms(lambda: ops.tail_gather(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R))
+        p = kernel_ms(lambda: ops.split_prologue(x, lin.w.had_kind, lin.R, lin.descending_rank, out=ws.pro))
+        per_linear[name] = {"gemm_ms": g, "tail_ms": t, "prologue_ms": p,
+                            "gemm_tops": 2.0 * M_TOKENS * N * K / (g * 1e-3) / 1e12,
+                            "tail_gflops": 2.0 * M_TOKENS * lin.R * N / (t * 1e-3) / 1e9}
+
+    # unfused bf16 cuBLAS linear of the same shapes (the GPU comparison line of the baseline)
+    bf16_ms = 0.0
+    for (name, K, N), x in zip(LAYER, xs):
+        Wb = torch.randn((N, K), device=dev, dtype=torch.bfloat16) * 0.02
+        bf16_ms += kernel_ms(lambda: torch.nn.functional.linear(x, Wb))
+        del Wb
+
+    peaks = load_peaks()
+    ops_step = layer_ops(M_TOKENS)
+    int8_peak = 2.0 * peaks["bf16_sustained"]  # no INT8 peak was measured: twice the sustained bf16 matmul figure
+    gemm_tops = ops_step / (t_gemm * 1e-3) / 1e12
+    pro_bytes = sum(M_TOKENS * (2 * K + K // 2 + 4 * lin.R + 4) for (_, K, _), lin in zip(LAYER, lins))
+    pro_gbs = pro_bytes / (t_pro * 1e-3) / 1e9
+    tail_flops = sum(2.0 * M_TOKENS * lin.R * N for (_, K, N), lin in zip(LAYER, lins))
+
+    h2d = sum(int(h.numel() * h.element_size()) for h in host_x)
+    d2h = sum(int(h.numel() * h.element_size()) for h in host_y)
+    line = {
+        "metric": METRIC,
+        "value": ops_step * world / (ms_step * 1e-3) / 1e12,
+        "unit": "TOPS",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "int4 x int4 -> int32 (tcgen05 kind::i8), fp32 dequant + bf16 tail, bf16 out",
+        "data": "synthetic",
+        "config": {"workload": "Qwen3-8B decoder layer linears: qkv 4096->6144, o 4096->4096, gate_up 4096->24576, "
+                               "down 12288->4096 (BASELINE configs[1])",
+                   "rows_per_gpu": M_TOKENS, "global_rows": M_TOKENS * world, "tail_ratio": RATIO,
+                   "parallelism": f"token-row shard x{world}, replicated weights, no collective",
+                   "l2": "per-step working set (96 MB int4 + 384 MB bf16 weights, 260 MB activations/outputs) exceeds the 126 MB L2"},
+        "e2e": {"value": ops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 12 * args.steps,
+        "clocks": clocks,
+        "roofline": {"kernel": "gemm_kernel<256> (tcgen05 kind::i8, fused dequant + tail add)", "bound": "tensor",
+                     "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
+                     "traffic": None,
+                     "peak_note": f"2 x sustained bf16 cuBLAS figure ({peaks['source']}); nominal dense INT8 {NOMINAL_INT8_TOPS}",
+                     "frac_of_nominal_int8": gemm_tops / NOMINAL_INT8_TOPS},
+        "kernels": {
+            "gemm": {"ms_per_step": t_gemm, "share": t_gemm / (t_gemm + t_tail + t_pro), "tops": gemm_tops},
+            "tail_gather": {"ms_per_step": t_tail, "share": t_tail / (t_gemm + t_tail + t_pro),
+                            "gflops": tail_flops / (t_tail * 1e-3) / 1e9, "bound": "CUDA-core fma + shared-memory gathers"},
+            "prologue": {"ms_per_step": t_pro, "share": t_pro / (t_gemm + t_tail + t_pro), "bound": "hbm",
+                         "achieved_gbs": pro_gbs, "peak_gbs": peaks["hbm_gbs"], "frac": pro_gbs / peaks["hbm_gbs"]},
+            "per_linear": per_linear,
+        },
+        "bf16_cublas_linear_ms_per_step": bf16_ms,
+        "split_over_bf16": ms_step / bf16_ms,
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        O, ws = cpu_oracle_setup()
+        cpu_oracle_step(O, ws)
+        t0 = time.perf_counter()
+        reps = 4
+        for _ in range(reps):
+            cpu_oracle_step(O, ws)
+        dt = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {
+            "value": layer_ops(CPU_SAMPLE_ROWS) / dt / 1e12, "unit": "TOPS", "cores": cpu_threads(), "kind": "port",
+            "sample": f"numpy oracle, online path of all four linears on {CPU_SAMPLE_ROWS} of the 2048 rows, mean of {reps} passes"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -275,6 +275,18 @@ class PreparedWeight:
     b_col: np.ndarray    # [N, K/2] uint8, K-contiguous per output channel
     b_row: np.ndarray    # [K, N/2] uint8, low nibble = even n
     w_scale: np.ndarray  # [N] f32
+    _codes_f64_t: Optional[np.ndarray] = None  # [K, N] float64 copy of the codes (cache for int_gemm)
+    _w_t_f32: Optional[np.ndarray] = None      # [K, N] float32 rotated weight (cache for tail_t16)
+
+    def codes_f64_t(self) -> np.ndarray:
+        if self._codes_f64_t is None:
+            self._codes_f64_t = np.ascontiguousarray(self.codes.T).astype(np.float64)
+        return self._codes_f64_t
+
+    def w_t_f32(self) -> np.ndarray:
+        if self._w_t_f32 is None:
+            self._w_t_f32 = np.ascontiguousarray(bf16_bits_to_f32(self.w_rot).T)
+        return self._w_t_f32
 
 
 def prepare_weight(w_bits: np.ndarray, kind: int, eps: float = EPS) -> PreparedWeight:
@@ -291,9 +303,11 @@ def prepare_weight(w_bits: np.ndarray, kind: int, eps: float = EPS) -> PreparedW
 
 
 # ----------------------------------------------------------------------------- GEMM + tail
-def int_gemm(qa: np.ndarray, qw: np.ndarray) -> np.ndarray:
-    """Exact int32 Qx . Qw^T (float64 BLAS is exact here: |sum| <= 64 K << 2^53)."""
-    acc = qa.astype(np.float64) @ qw.astype(np.float64).T
+def int_gemm(qa: np.ndarray, qw) -> np.ndarray:
+    """Exact int32 Qx . Qw^T (float64 BLAS is exact here: |sum| <= 64 K << 2^53).
+    `qw` is an [N,K] int8 array or a PreparedWeight (whose float64 copy is cached)."""
+    wt = qw.codes_f64_t() if isinstance(qw, PreparedWeight) else qw.astype(np.float64).T
+    acc = qa.astype(np.float64) @ wt
     return np.rint(acc).astype(np.int32)
 
 
@@ -303,12 +317,16 @@ def dequant(acc: np.ndarray, s_x: np.ndarray, s_w: np.ndarray) -> np.ndarray:
     return (d * s_w.astype(np.float32).reshape(1, -1)).astype(np.float32)
 
 
-def tail_t16(idx: np.ndarray, tail_val_bits: np.ndarray, w_rot_bits: np.ndarray) -> np.ndarray:
+def tail_t16(idx: np.ndarray, tail_val_bits: np.ndarray, w_rot_bits) -> np.ndarray:
     """sum_r x_tail[m,r] * W_rot[n, idx[m,r]] as a left-to-right fp32 fma chain in ascending
-    index order.  bf16 x bf16 is exact in fp32, so fma(x, w, acc) == fl(acc + x*w)."""
+    index order.  bf16 x bf16 is exact in fp32, so fma(x, w, acc) == fl(acc + x*w).
+    `w_rot_bits` is an [N,K] bf16-bit array or a PreparedWeight."""
     M, R = idx.shape
-    N = w_rot_bits.shape[0]
-    wt = np.ascontiguousarray(bf16_bits_to_f32(w_rot_bits).T)  # [K, N]
+    if isinstance(w_rot_bits, PreparedWeight):
+        wt = w_rot_bits.w_t_f32()
+    else:
+        wt = np.ascontiguousarray(bf16_bits_to_f32(w_rot_bits).T)  # [K, N]
+    N = wt.shape[1]
     xv = bf16_bits_to_f32(tail_val_bits)
     acc = np.zeros((M, N), dtype=np.float32)
     for r in range(R):
@@ -320,10 +338,10 @@ def split_linear_t16(x_bits: np.ndarray, w: PreparedWeight, kind: int, R: int,
                      bias: Optional[np.ndarray] = None, descending_rank: Optional[int] = None):
     """Full path, tail mode T16.  Returns (bf16 bits [M,N], fp32 pre-rounding, Prologue, int32 acc)."""
     p = prologue(x_bits, kind, R, descending_rank)
-    acc = int_gemm(p.codes, w.codes)
+    acc = int_gemm(p.codes, w)
     y = dequant(acc, p.body_scale, w.w_scale)
     if R:
-        y = (y + tail_t16(p.idx, p.tail_val, w.w_rot)).astype(np.float32)
+        y = (y + tail_t16(p.idx, p.tail_val, w)).astype(np.float32)
     if bias is not None:
         y = (y + bias.astype(np.float32).reshape(1, -1)).astype(np.float32)
     return f32_to_bf16_bits(y), y, p, acc

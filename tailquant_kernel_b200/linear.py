@@ -111,6 +111,8 @@ def split_linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[t
     tensor is a per-layer workspace that the next call of the same layer overwrites."""
     if split_ratio is not None:
         ratio = split_ratio
+    if bias is not None and not torch.is_tensor(bias):  # the adapter's positional form fn(x, W, ratio)
+        ratio, bias = float(bias), None
     if weight.dim() != 2 or x.shape[-1] != weight.shape[1]:
         raise RuntimeError(f"weight must be [N, K] with K = x.shape[-1]; got {tuple(weight.shape)} for x {tuple(x.shape)}")
     key = (weight.data_ptr(), weight._version, tuple(weight.shape), float(ratio),
