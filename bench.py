@@ -189,7 +189,8 @@ def run_ours(args) -> None:
     for i, (name, K, N) in enumerate(LAYER):
         gen.manual_seed(100 + i)
         W = (torch.randn((N, K), generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(dev)
-        lin = SplitLinear(W, ratio=RATIO, had_kind=TQ_HAD_KRON12 if K == 12288 else TQ_HAD_WHT)
+        lin = SplitLinear(W, ratio=RATIO, had_kind=TQ_HAD_KRON12 if K == 12288 else TQ_HAD_WHT,
+                          tail_engine=args.tail_engine)
         del W
         gen.manual_seed(1000 * (rank + 1) + i)
         x = torch.randn((M_TOKENS, K), generator=gen, dtype=torch.float32)
@@ -252,47 +253,68 @@ def run_ours(args) -> None:
         return e0.elapsed_time(e1) / reps
 
     wss = [lin.workspace(M_TOKENS) for lin in lins]
+    mma = args.tail_engine == "mma"
 
-    def all_prologue():
-        for lin, x, ws in zip(lins, xs, wss):
-            ops.split_prologue(x, lin.w.had_kind, lin.R, lin.descending_rank, out=ws.pro)
+    def pro_call(lin, x, ws):
+        return lambda: ops.split_prologue(x, lin.w.had_kind, lin.R, lin.descending_rank, out=ws.pro)
 
-    def all_tail():
-        for lin, ws in zip(lins, wss):
-            ops.tail_gather(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R)
+    def tail_call(lin, ws):
+        return lambda: ops.tail_gather(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R)
 
-    def all_gemm():
-        for lin, ws in zip(lins, wss):
-            ops.split_gemm_fused(ws.pro.a_pack, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out, tail=ws.tail)
+    def gemm_call(lin, ws):
+        if mma:
+            return lambda: ops.split_gemm_mma(ws.pro.a_q8, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out,
+                                              w_rot=lin.w.w_rot, tail_idx=ws.pro.tail_idx, tail_val=ws.pro.tail_val,
+                                              R=lin.R)
+        return lambda: ops.split_gemm_fused(ws.pro.a_pack, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out,
+                                            tail=ws.tail)
 
-    t_pro, t_tail, t_gemm = kernel_ms(all_prologue), kernel_ms(all_tail), kernel_ms(all_gemm)
+    def run_all(calls):
+        def f():
+            for c in calls:
+                c()
+        return f
+
+    t_pro = kernel_ms(run_all([pro_call(l, x, w) for l, x, w in zip(lins, xs, wss)]))
+    t_gemm = kernel_ms(run_all([gemm_call(l, w) for l, w in zip(lins, wss)]))
+    t_tail = 0.0 if mma else kernel_ms(run_all([tail_call(l, w) for l, w in zip(lins, wss)]))
     per_linear = {}
     for (name, K, N), lin, x, ws in zip(LAYER, lins, xs, wss):
-        g = kernel_ms(lambda: ops.split_gemm_fused(ws.pro.a_pack, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out,
-                                                   tail=ws.tail))
-        t = kernel_ms(lambda: ops.tail_gather(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R))
-        p = kernel_ms(lambda: ops.split_prologue(x, lin.w.had_kind, lin.R, lin.descending_rank, out=ws.pro))
-        per_linear[name] = {"gemm_ms": g, "tail_ms": t, "prologue_ms": p,
-                            "gemm_tops": 2.0 * M_TOKENS * N * K / (g * 1e-3) / 1e12,
-                            "tail_gflops": 2.0 * M_TOKENS * lin.R * N / (t * 1e-3) / 1e9}
+        g = kernel_ms(gemm_call(lin, ws))
+        pr = kernel_ms(pro_call(lin, x, ws))
+        per_linear[name] = {"gemm_ms": g, "prologue_ms": pr, "gemm_tops": 2.0 * M_TOKENS * N * K / (g * 1e-3) / 1e12}
+        if not mma:
+            tl = kernel_ms(tail_call(lin, ws))
+            per_linear[name].update({"tail_ms": tl, "tail_gflops": 2.0 * M_TOKENS * lin.R * N / (tl * 1e-3) / 1e9})
 
-    # unfused bf16 cuBLAS linear of the same shapes (the GPU comparison line of the baseline)
-    bf16_ms = 0.0
+    # comparison lines on the same shapes: unfused bf16 cuBLAS linear (the baseline's GPU comparison) and
+    # int8 cuBLAS (torch._int_mm), the best dense INT8 rate a library reaches on this box
+    bf16_ms, int8_ms = 0.0, 0.0
     for (name, K, N), x in zip(LAYER, xs):
         Wb = torch.randn((N, K), device=dev, dtype=torch.bfloat16) * 0.02
         bf16_ms += kernel_ms(lambda: torch.nn.functional.linear(x, Wb))
         del Wb
+        a8 = torch.randint(-8, 8, (M_TOKENS, K), dtype=torch.int8, device=dev)
+        b8 = torch.randint(-8, 8, (N, K), dtype=torch.int8, device=dev).t()
+        int8_ms += kernel_ms(lambda: torch._int_mm(a8, b8))
+        del a8, b8
 
     peaks = load_peaks()
     ops_step = layer_ops(M_TOKENS)
     int8_peak = 2.0 * peaks["bf16_sustained"]  # no INT8 peak was measured: twice the sustained bf16 matmul figure
     gemm_tops = ops_step / (t_gemm * 1e-3) / 1e12
-    pro_bytes = sum(M_TOKENS * (2 * K + K // 2 + 4 * lin.R + 4) for (_, K, _), lin in zip(LAYER, lins))
+    pro_bytes = sum(M_TOKENS * (2 * K + (K if mma else K // 2) + 4 * lin.R + 4) for (_, K, _), lin in zip(LAYER, lins))
     pro_gbs = pro_bytes / (t_pro * 1e-3) / 1e9
     tail_flops = sum(2.0 * M_TOKENS * lin.R * N for (_, K, N), lin in zip(LAYER, lins))
+    # tensor-pipe time the kernel's MMAs need at the measured library rates: the int8 product, plus (tensor-core
+    # tail) a dense bf16 product of the same shape over the zero-filled tail matrix
+    pipe_ms = ops_step / (int8_peak * 1e12) * 1e3 + (ops_step / (peaks["bf16_sustained"] * 1e12) * 1e3 if mma else 0.0)
+    t_sum = t_gemm + t_tail + t_pro
 
     h2d = sum(int(h.numel() * h.element_size()) for h in host_x)
     d2h = sum(int(h.numel() * h.element_size()) for h in host_y)
+    kname = ("split_gemm_kernel<256> (tcgen05 kind::i8 dense + kind::f16 tail, fused dequant)" if mma
+             else "gemm_kernel<256> (tcgen05 kind::i8, fused dequant + tail add)")
     line = {
         "metric": METRIC,
         "value": ops_step * world / (ms_step * 1e-3) / 1e12,
@@ -304,33 +326,40 @@ def run_ours(args) -> None:
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "int4 x int4 -> int32 (tcgen05 kind::i8), fp32 dequant + bf16 tail, bf16 out",
+        "dtype": "int4 x int4 -> int32 (tcgen05 kind::i8), bf16 tail, fp32 dequant, bf16 out",
         "data": "synthetic",
         "config": {"workload": "Qwen3-8B decoder layer linears: qkv 4096->6144, o 4096->4096, gate_up 4096->24576, "
                                "down 12288->4096 (BASELINE configs[1])",
                    "rows_per_gpu": M_TOKENS, "global_rows": M_TOKENS * world, "tail_ratio": RATIO,
+                   "tail_engine": args.tail_engine,
                    "parallelism": f"token-row shard x{world}, replicated weights, no collective",
-                   "l2": "per-step working set (96 MB int4 + 384 MB bf16 weights, 260 MB activations/outputs) exceeds the 126 MB L2"},
+                   "l2": "per-step working set (96 MB int4 + 192 MB bf16 weights, 260 MB activations/outputs) exceeds the 126 MB L2"},
         "e2e": {"value": ops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 12 * args.steps,
+        "gpu_launches": (8 if mma else 12) * args.steps,
         "clocks": clocks,
-        "roofline": {"kernel": "gemm_kernel<256> (tcgen05 kind::i8, fused dequant + tail add)", "bound": "tensor",
+        "roofline": {"kernel": kname, "bound": "tensor",
                      "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
                      "traffic": None,
-                     "peak_note": f"2 x sustained bf16 cuBLAS figure ({peaks['source']}); nominal dense INT8 {NOMINAL_INT8_TOPS}",
-                     "frac_of_nominal_int8": gemm_tops / NOMINAL_INT8_TOPS},
+                     "peak_note": f"2 x sustained bf16 cuBLAS figure ({peaks['source']}); nominal dense INT8 {NOMINAL_INT8_TOPS}; "
+                                  "achieved counts the algorithmic 2*M*N*K of the INT4 product only",
+                     "frac_of_nominal_int8": gemm_tops / NOMINAL_INT8_TOPS,
+                     "tensor_pipe_ms_at_library_rates": pipe_ms, "frac_of_library_rate_pipe_time": pipe_ms / t_gemm,
+                     "int8_cublas_same_shapes_tops": ops_step / (int8_ms * 1e-3) / 1e12},
         "kernels": {
-            "gemm": {"ms_per_step": t_gemm, "share": t_gemm / (t_gemm + t_tail + t_pro), "tops": gemm_tops},
-            "tail_gather": {"ms_per_step": t_tail, "share": t_tail / (t_gemm + t_tail + t_pro),
-                            "gflops": tail_flops / (t_tail * 1e-3) / 1e9, "bound": "CUDA-core fma + shared-memory gathers"},
-            "prologue": {"ms_per_step": t_pro, "share": t_pro / (t_gemm + t_tail + t_pro), "bound": "hbm",
+            "gemm": {"ms_per_step": t_gemm, "share": t_gemm / t_sum, "tops": gemm_tops},
+            "prologue": {"ms_per_step": t_pro, "share": t_pro / t_sum, "bound": "hbm",
                          "achieved_gbs": pro_gbs, "peak_gbs": peaks["hbm_gbs"], "frac": pro_gbs / peaks["hbm_gbs"]},
             "per_linear": per_linear,
         },
         "bf16_cublas_linear_ms_per_step": bf16_ms,
+        "int8_cublas_gemm_ms_per_step": int8_ms,
         "split_over_bf16": ms_step / bf16_ms,
     }
+    if not mma:
+        line["kernels"]["tail_gather"] = {"ms_per_step": t_tail, "share": t_tail / t_sum,
+                                          "gflops": tail_flops / (t_tail * 1e-3) / 1e9,
+                                          "bound": "CUDA-core fma + shared-memory gathers"}
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         O, ws = cpu_oracle_setup()
@@ -356,6 +385,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tail-engine", default="mma", choices=["mma", "gather"],
+                    help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

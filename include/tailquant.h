@@ -57,6 +57,9 @@ const char* tq_last_cuda_error(void);
  *   descending_rank  1-based rank (in |x| descending order, ties by lowest index) whose
  *                magnitude sets the body scale; R+1 = absmax of the body
  *   a_pack       [M,K/2] u8 : element 2i -> low nibble, 2i+1 -> high nibble; tail positions 0
+ *                (may be NULL when a_q8 is given)
+ *   a_q8         [M,K] i8 : the same codes, one per byte, the even elements of every 8-group
+ *                first and then the odd ones -- the operand format of tq_split_gemm_mma (may be NULL)
  *   body_scale   [M] f32 = max(|x|_(rank), eps) / 7
  *   top_scale    [M] f32 = max(|x|_max, eps) / 7                     (may be NULL)
  *   tail_idx16   [M,tail_ld] u16 ascending channel indices, R per row (tail mode T16; may be NULL)
@@ -67,7 +70,7 @@ const char* tq_last_cuda_error(void);
  *   x_rot        [M,K] bf16 rotated activations                      (debug / weight prep; may be NULL)
  */
 int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank, float eps,
-                      uint8_t* a_pack, float* body_scale, float* top_scale,
+                      uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale,
                       uint16_t* tail_idx16, void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q,
                       void* x_rot, void* stream);
 
@@ -122,6 +125,20 @@ int tq_int4_matmul(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int 
 int tq_split_gemm_fused(const uint8_t* a_pack, const float* body_scale, const uint8_t* b_col,
                         const float* w_scale, const float* tail, const float* bias, void* out_bf16,
                         int M, int N, int K, void* stream);
+
+/* The same linear in ONE kernel with the tail on the tensor cores: the dense part runs on tcgen05
+ * kind::i8, the tail as a bf16 MMA (fp32 accumulation in tensor memory) over the zero-filled tail
+ * matrix that the kernel builds in shared memory from the (index, value) lists.  The INT4 codes,
+ * indices and int32 accumulators are the same bits as on the other path; the tail sum is an fp32
+ * tensor-core accumulation instead of the fixed-order fma chain of tq_tail_gather, so the bf16 output
+ * can differ from that path in the last bit.  Has the role of the reference's fused-epilogue
+ * prototypes (tools/quarot_split_fused_epilogue_ext_v1.py:283-432).
+ *   a_q8      [M,K] i8 from tq_split_prologue       w_rot  [N,K] bf16 from tq_prepare_weight (R > 0)
+ *   dbg_acc   optional [M,N] i32: accumulators      dbg_tail  optional [M,N] f32: tail sums */
+int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
+                      const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
+                      const void* tail_val, int tail_ld, int R, const float* bias, void* out_bf16,
+                      int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream);
 
 /* Finisher of the split-K path: out = bf16((float(C)*body_scale[m])*w_scale[n] + tail + bias). */
 int tq_dequant_finish(const int32_t* C, const float* body_scale, const float* w_scale,

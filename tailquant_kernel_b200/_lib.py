@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtailquant.so")
+# TAILQUANT_LIB may point at another build of the same C ABI (e.g. an instrumented one)
+LIB_PATH = os.environ.get("TAILQUANT_LIB") or os.path.join(HERE, "libtailquant.so")
 
 TQ_HAD_NONE, TQ_HAD_WHT, TQ_HAD_KRON12, TQ_HAD_BLOCK128 = 0, 1, 2, 3
 TQ_BF16, TQ_FP16 = 0, 1
@@ -20,7 +21,8 @@ SIGNATURES = {
     "tq_version": [],
     "tq_error_string": [_I],
     "tq_last_cuda_error": [],
-    "tq_split_prologue": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P],
+    "tq_split_prologue": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P],
+    "tq_split_gemm_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P],
     "tq_topr_pack": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P],
     "tq_prepare_weight": [_P, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P],
     "tq_int4_matmul": [_P, _P, _P, _I, _I, _I, _I, _P],

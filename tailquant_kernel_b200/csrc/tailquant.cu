@@ -3,5 +3,6 @@
 #include "tq_api.cu"
 #include "tq_prologue.cu"
 #include "tq_gemm.cu"
+#include "tq_gemm_tail.cu"
 #include "tq_tail.cu"
 #include "tq_misc.cu"

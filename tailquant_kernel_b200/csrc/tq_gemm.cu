@@ -67,38 +67,6 @@ struct Smem {
   static constexpr int DYN = TOTAL + 1024;  // slack to align the base to 1024 bytes
 };
 
-// K-major operand tile, rows of 128 bytes, 8-row groups 1024 bytes apart, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);   // start address
-  d |= (uint64_t)0 << 16;                     // leading byte offset: unused for swizzled K-major
-  d |= (uint64_t)(1024u >> 4) << 32;          // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                     // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
-  return d;
-}
-
-template <int BN>
-__device__ __forceinline__ constexpr uint32_t make_idesc() {
-  return (2u << 4)                    // D = S32
-         | (1u << 7) | (1u << 10)     // A, B = signed 8-bit
-         | ((uint32_t)(BN >> 3) << 17)
-         | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 struct TileCoord {
   int mt, nt, kb0, nkb;
 };
@@ -187,7 +155,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc<BN>();
+      constexpr uint32_t idesc = make_idesc_i8<BN>();
       int su = 0, as = 0;
       uint32_t phu = 0, pha = 0;
       bool ok = true;

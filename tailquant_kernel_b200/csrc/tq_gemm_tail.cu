@@ -1,0 +1,439 @@
+// Split GEMM with the tail on the tensor cores (sm_100a): one kernel computes
+//   out[m,n] = bf16( (float(sum_k qx[m,k] qw[n,k]) * s_x[m]) * s_w[n]  +  sum_r x_tail[m,r] W_rot[n, idx[m,r]]  + bias[n] )
+// with the dense part on tcgen05 kind::i8 (int32 accumulator in tensor memory) and the tail on tcgen05
+// kind::f16 (bf16 x bf16, fp32 accumulator in tensor memory) over the zero-filled tail matrix.
+//
+// Why not gather: after the rotation the tail positions are spread uniformly over K, so the gathered
+// form is M*R*N scalar multiply-adds with no operand reuse; on this GPU the dense bf16 MMA over a K-wide,
+// 95 %-zero A operand is several times faster than that at ratio 0.05.  The exact-order gather kernel
+// (tq_tail.cu) stays available as the bit-exact mode.
+//
+// One persistent CTA per SM.  For every 128-wide slice of K a tile consumes three operand slots:
+//   slot kind        A operand [128 rows]                         B operand [BN rows]
+//   int8  (128 k)    INT8 codes of the activations, TMA           INT4 weights: TMA to staging, widened to
+//                    (128-byte swizzle) straight into the slot    INT8 (x16) by the builder warps
+//   bf16  (64 k) x2  tail values scattered by the builder warps   rotated bf16 weight rows [N,K], TMA
+//                    from the rows' (index, value) lists into a    (128-byte swizzle) straight into the slot
+//                    zero-filled tile
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (+ tensor-memory allocation), 2..5 = epilogue,
+// 6..13 = builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory (no multicast).
+// Every mbarrier wait is bounded (see mbar_wait).
+//
+// The activation codes arrive as INT8 with the two nibble planes of each 8-element group de-interleaved
+// ([0,2,4,6,1,3,5,7]), which is the order the builders' widening of the weights produces, so both
+// operands see the same permutation of K and the dot product is unchanged.  Weights carry a factor 16
+// (the nibble is kept in the top half of the byte, which makes it sign-correct without an extension),
+// removed by an exact >> 4 of the accumulator.
+//
+// Reference behaviour covered: GEMM + dequant + sparse correction in one kernel, i.e. what the reference
+// prototypes in tools/quarot_split_fused_epilogue_ext_v1.py:283-432 and
+// tools/qfactory_split_fused_epilogue_v1.py:153-233 (there with an INT4 tail and R fixed at compile time).
+#include "tq_common.cuh"
+#include "tq_ptx.cuh"
+
+namespace tq {
+namespace {
+
+constexpr int G_BM = 128;
+constexpr int G_BK = 128;
+constexpr int G_BUILD_WARPS = 8;
+constexpr int G_NBT = G_BUILD_WARPS * 32;  // builder threads
+constexpr int G_THREADS = (6 + G_BUILD_WARPS) * 32;
+constexpr int G_SENT = 0x7fffffff;
+
+struct SplitGemmParams {
+  int M, N, K, R, ld;
+  int tiles_m, tiles_n, kb_total, has_tail;
+  const uint16_t* idx;
+  const uint16_t* val;
+  const float* sx;
+  const float* sw;
+  const float* bias;
+  __nv_bfloat16* out;
+  int32_t* dbg_acc;   // optional [M,N]: the int32 accumulators
+  float* dbg_tail;    // optional [M,N]: the fp32 tail sums
+};
+
+template <int BN>
+struct GS {
+  static constexpr int SU = 4;                            // operand slots
+  static constexpr int SP = 2;                            // packed-weight staging buffers
+  static constexpr int SLOT = (G_BM + BN) * 128;          // A region (16 KB) then B region
+  static constexpr int B_OFF = G_BM * 128;
+  static constexpr int STAGE = BN * (G_BK / 2);
+  static constexpr int STAGE_OFF = SU * SLOT;
+  static constexpr int BAR_OFF = STAGE_OFF + SP * STAGE;
+  static constexpr int NUM_BARS = 2 * SP + 2 * SU + 2;
+  static constexpr int DYN = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(G_THREADS, 1)
+split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_constant__ CUtensorMap tmap_b4,
+                  const __grid_constant__ CUtensorMap tmap_w, const SplitGemmParams p) {
+  using S = GS<BN>;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_dyn + (base - raw);
+
+  const uint32_t bars = base + S::BAR_OFF;
+  auto full_p = [&](int s) { return bars + 8u * s; };
+  auto empty_p = [&](int s) { return bars + 8u * (S::SP + s); };
+  auto full_u = [&](int s) { return bars + 8u * (2 * S::SP + s); };
+  auto empty_u = [&](int s) { return bars + 8u * (2 * S::SP + S::SU + s); };
+  const uint32_t acc_full = bars + 8u * (2 * S::SP + 2 * S::SU);
+  const uint32_t acc_empty = acc_full + 8u;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + S::BAR_OFF + S::NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + S::BAR_OFF + S::NUM_BARS * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const bool has_tail = p.has_tail != 0;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // int32 accumulator, then fp32 tail accumulator
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a8)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b4)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+    for (int s = 0; s < S::SP; ++s) {
+      mbar_init(full_p(s), 1);
+      mbar_init(empty_p(s), G_NBT);
+    }
+    for (int s = 0; s < S::SU; ++s) {
+      mbar_init(full_u(s), G_NBT + 1);  // every builder thread + the producer's expect_tx arrival
+      mbar_init(empty_u(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 128);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // slot use number q -> (slot, parity)
+  auto slot_of = [](int q) { return q % S::SU; };
+  auto par_of = [](int q) { return (uint32_t)((q / S::SU) & 1); };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int q = 0, sp = 0;
+      uint32_t php = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const int mt = t % p.tiles_m, nt = t / p.tiles_m;
+        for (int kb = 0; kb < p.kb_total; ++kb) {
+          if (!(ok = mbar_wait(empty_p(sp), php ^ 1u, abort_flag, 0x1000u))) break;
+          mbar_arrive_expect_tx(full_p(sp), S::STAGE);
+          tma_load_2d(base + S::STAGE_OFF + sp * S::STAGE, &tmap_b4, kb * (G_BK / 2), nt * BN, full_p(sp));
+          if (++sp == S::SP) {
+            sp = 0;
+            php ^= 1u;
+          }
+          {
+            const int s = slot_of(q);
+            if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x2000u))) break;
+            mbar_arrive_expect_tx(full_u(s), G_BM * 128);
+            tma_load_2d(base + s * S::SLOT, &tmap_a8, kb * G_BK, mt * G_BM, full_u(s));
+            ++q;
+          }
+          if (has_tail) {
+            for (int h = 0; h < 2 && ok; ++h) {
+              const int s = slot_of(q);
+              if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x4000u))) break;
+              mbar_arrive_expect_tx(full_u(s), BN * 128);
+              tma_load_2d(base + s * S::SLOT + S::B_OFF, &tmap_w, kb * G_BK + h * 64, nt * BN, full_u(s));
+              ++q;
+            }
+            if (!ok) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_i8 = make_idesc_i8<BN>();
+      constexpr uint32_t idesc_bf = make_idesc_bf16<BN>();
+      int q = 0;
+      uint32_t pha = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        if (!(ok = mbar_wait(acc_empty, pha ^ 1u, abort_flag, 0x8000u))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < p.kb_total && ok; ++kb) {
+          {
+            const int s = slot_of(q);
+            if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x10000u))) break;
+            tc_fence_after();
+            const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_i8(tmem_base, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_i8,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit(empty_u(s));
+            ++q;
+          }
+          if (has_tail) {
+            for (int h = 0; h < 2; ++h) {
+              const int s = slot_of(q);
+              if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x20000u))) break;
+              tc_fence_after();
+              const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                umma_bf16(tmem_base + BN, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_bf,
+                          (kb > 0 || h > 0 || k > 0) ? 1u : 0u);
+              umma_commit(empty_u(s));
+              ++q;
+            }
+          }
+        }
+        if (!ok) break;
+        umma_commit(acc_full);
+        pha ^= 1u;
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;
+    uint32_t pha = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      const int mt = t % p.tiles_m, nt = t / p.tiles_m;
+      if (!(ok = mbar_wait(acc_full, pha, abort_flag, 0x40000u))) break;
+      tc_fence_after();
+      const int row = mt * G_BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sx = row_ok ? p.sx[row] : 0.0f;
+      const size_t rowoff = (size_t)row * p.N;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t ri[32], rf[32];
+        __syncwarp();
+        tmem_ld32(lane_addr + (uint32_t)c0, ri);
+        if (has_tail) {
+          tmem_ld32(lane_addr + (uint32_t)(BN + c0), rf);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) rf[i] = 0u;
+        }
+        const int n0 = nt * BN + c0;
+        if (!row_ok || n0 >= p.N) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + 8 * j;
+          if (n < p.N) {
+            float d[8];
+            const float4 w0 = *reinterpret_cast<const float4*>(p.sw + n);
+            const float4 w1 = *reinterpret_cast<const float4*>(p.sw + n + 4);
+            const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float dense = __fmul_rn(__fmul_rn((float)((int)ri[8 * j + i] >> 4), sx), ws[i]);
+              d[i] = has_tail ? __fadd_rn(dense, __uint_as_float(rf[8 * j + i])) : dense;
+            }
+            if (p.bias) {
+              const float4 b0 = *reinterpret_cast<const float4*>(p.bias + n);
+              const float4 b1 = *reinterpret_cast<const float4*>(p.bias + n + 4);
+              const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], bs[i]);
+            }
+            uint4 o;
+            o.x = f32_to_bf16_bits(d[0]) | (f32_to_bf16_bits(d[1]) << 16);
+            o.y = f32_to_bf16_bits(d[2]) | (f32_to_bf16_bits(d[3]) << 16);
+            o.z = f32_to_bf16_bits(d[4]) | (f32_to_bf16_bits(d[5]) << 16);
+            o.w = f32_to_bf16_bits(d[6]) | (f32_to_bf16_bits(d[7]) << 16);
+            *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+            if (p.dbg_acc) {
+              *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n) =
+                  make_int4((int)ri[8 * j] >> 4, (int)ri[8 * j + 1] >> 4, (int)ri[8 * j + 2] >> 4, (int)ri[8 * j + 3] >> 4);
+              *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n + 4) =
+                  make_int4((int)ri[8 * j + 4] >> 4, (int)ri[8 * j + 5] >> 4, (int)ri[8 * j + 6] >> 4, (int)ri[8 * j + 7] >> 4);
+            }
+            if (p.dbg_tail) {
+              *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n) = make_uint4(rf[8 * j], rf[8 * j + 1], rf[8 * j + 2], rf[8 * j + 3]);
+              *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n + 4) = make_uint4(rf[8 * j + 4], rf[8 * j + 5], rf[8 * j + 6], rf[8 * j + 7]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty);
+      pha ^= 1u;
+    }
+  } else {
+    // ------------------------------------------------------------------ builders
+    const int btid = threadIdx.x - 6 * 32;
+    const int half = btid >> 7, brow = btid & 127;  // tail tiles: one thread per row and 64-wide half
+    int q = 0, sp = 0;
+    uint32_t php = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      const int mt = t % p.tiles_m;
+      const int grow = mt * G_BM + brow;
+      const uint16_t* irow = p.idx + (size_t)grow * p.ld;
+      const uint16_t* vrow = p.val + (size_t)grow * p.ld;
+      int cur = 0, kk = G_SENT;
+      uint32_t xx = 0;
+      if (has_tail && grow < p.M && p.R > 0) {
+        kk = (int)__ldg(irow);
+        xx = (uint32_t)__ldg(vrow);
+      }
+      for (int kb = 0; kb < p.kb_total; ++kb) {
+        {  // INT4 -> INT8 (x16) of the weight tile
+          const int s = slot_of(q);
+          if (!(ok = mbar_wait(full_p(sp), php, abort_flag, 0x80000u))) break;
+          if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u))) break;
+          tc_fence_after();
+          const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
+          unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
+#pragma unroll
+          for (int task = btid; task < BN * 4; task += G_NBT) {
+            const int row = task >> 2, piece = task & 3;
+            const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
+            unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
+            uint4 lo, hi;
+            lo.x = (w.x << 4) & 0xf0f0f0f0u;
+            lo.y = w.x & 0xf0f0f0f0u;
+            lo.z = (w.y << 4) & 0xf0f0f0f0u;
+            lo.w = w.y & 0xf0f0f0f0u;
+            hi.x = (w.z << 4) & 0xf0f0f0f0u;
+            hi.y = w.z & 0xf0f0f0f0u;
+            hi.z = (w.w << 4) & 0xf0f0f0f0u;
+            hi.w = w.w & 0xf0f0f0f0u;
+            *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
+            *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(full_u(s));
+          mbar_arrive(empty_p(sp));
+          if (++sp == S::SP) {
+            sp = 0;
+            php ^= 1u;
+          }
+          ++q;
+        }
+        if (has_tail) {  // zero-filled bf16 tail tiles of the two 64-wide halves of this K slice
+          const int sa = slot_of(q), sb = slot_of(q + 1);
+          if (!(ok = mbar_wait(empty_u(sa), par_of(q) ^ 1u, abort_flag, 0x200000u))) break;
+          if (!(ok = mbar_wait(empty_u(sb), par_of(q + 1) ^ 1u, abort_flag, 0x400000u))) break;
+          tc_fence_after();
+          unsigned char* arow = sm + (half ? sb : sa) * S::SLOT + (brow >> 3) * 1024 + (brow & 7) * 128;
+          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + (c << 4)) = z;
+          const int kbase = kb * G_BK + half * 64;
+          while (kk < kbase + 64) {
+            if (kk >= kbase) {
+              const int c = kk - kbase;
+              *reinterpret_cast<uint16_t*>(arow + ((((c >> 3) ^ (brow & 7))) << 4) + (c & 7) * 2) = (uint16_t)xx;
+            }
+            if (++cur < p.R) {
+              kk = (int)__ldg(irow + cur);
+              xx = (uint32_t)__ldg(vrow + cur);
+            } else {
+              kk = G_SENT;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(full_u(sa));
+          mbar_arrive(full_u(sb));
+          q += 2;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <int BN>
+int launch_split_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot, SplitGemmParams p, cudaStream_t st) {
+  using S = GS<BN>;
+  auto kern = split_gemm_kernel<BN>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(dev < 64 && configured[dev])) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return TQ_ERR_CUDA;
+    }
+    if (dev < 64) configured[dev] = true;
+  }
+  CUtensorMap ma, mb, mw;
+  if (!make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_q8, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)p.K, 128,
+                          G_BM, true))
+    return TQ_ERR_CUDA;
+  if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_col, (uint64_t)(p.K / 2), (uint64_t)p.N,
+                          (uint64_t)(p.K / 2), G_BK / 2, BN))
+    return TQ_ERR_CUDA;
+  // without a tail the bf16 map is never used; point it at the packed weights to keep it valid
+  const void* wsrc = p.has_tail ? w_rot : (const void*)b_col;
+  if (!make_tensor_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, wsrc, (uint64_t)(p.has_tail ? p.K : p.K / 4),
+                          (uint64_t)p.N, (uint64_t)(p.has_tail ? p.K * 2 : p.K / 2), 64, BN, true))
+    return TQ_ERR_CUDA;
+  p.tiles_m = (p.M + G_BM - 1) / G_BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.kb_total = p.K / G_BK;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int total = p.tiles_m * p.tiles_n;
+  const int grid = total < sms ? total : sms;
+  kern<<<grid, G_THREADS, S::DYN, st>>>(ma, mb, mw, p);
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
+                                 const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
+                                 const void* tail_val, int tail_ld, int R, const float* bias, void* out_bf16,
+                                 int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream) {
+  using namespace tq;
+  if (!a_q8 || !body_scale || !b_col || !w_scale || !out_bf16 || M < 0 || N <= 0 || K <= 0 || R < 0 || R >= K)
+    return TQ_ERR_BAD_ARG;
+  if (R > 0 && (!w_rot || !tail_idx16 || !tail_val || tail_ld < R)) return TQ_ERR_BAD_ARG;
+  if (K % G_BK != 0 || N % 8 != 0 || K > 65536) return TQ_ERR_UNSUPPORTED;
+  if (!aligned16(a_q8) || !aligned16(b_col) || !aligned16(out_bf16) || !aligned16(w_scale) ||
+      (R > 0 && !aligned16(w_rot)) || (bias && !aligned16(bias)) || (dbg_acc && !aligned16(dbg_acc)) ||
+      (dbg_tail && !aligned16(dbg_tail)))
+    return TQ_ERR_MISALIGNED;
+  if (M == 0) return TQ_OK;
+  SplitGemmParams p = {};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.R = R;
+  p.ld = tail_ld;
+  p.has_tail = R > 0 ? 1 : 0;
+  p.idx = tail_idx16;
+  p.val = reinterpret_cast<const uint16_t*>(tail_val);
+  p.sx = body_scale;
+  p.sw = w_scale;
+  p.bias = bias;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  p.dbg_acc = dbg_acc;
+  p.dbg_tail = dbg_tail;
+  const long tiles256 = (long)((M + G_BM - 1) / G_BM) * ((N + 255) / 256);
+  if (tiles256 >= 148) return launch_split_gemm<256>(a_q8, b_col, w_rot, p, (cudaStream_t)stream);
+  return launch_split_gemm<128>(a_q8, b_col, w_rot, p, (cudaStream_t)stream);
+}

@@ -34,6 +34,7 @@ struct PrologueParams {
   float eps, hscale;
   int scale_mode;  // 0: max(t, eps) / 7 (activations); 1: max(t / 7, eps) (weights)
   uint8_t* a_pack;
+  int8_t* a_q8;
   float* body_scale;
   float* top_scale;
   uint16_t* tail_idx16;
@@ -233,6 +234,7 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
   uint16_t* bm_gt = reinterpret_cast<uint16_t*>(smem_raw + K / 2);
   uint16_t* bm_eq = reinterpret_cast<uint16_t*>(smem_raw + K / 2 + K / 8);
   uint32_t* prefix = reinterpret_cast<uint32_t*>(smem_raw + K / 2 + K / 4);
+  int8_t* q8_s = reinterpret_cast<int8_t*>(smem_raw + K);  // [K] INT8 codes in GEMM operand order
   unsigned char* after = smem_raw + (size_t)K * 4;
   uint32_t* hist = reinterpret_cast<uint32_t*>(after);
   uint32_t* red = hist + 128;
@@ -418,8 +420,14 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
           }
         }
       }
-      const uint32_t nib = is_tail ? 0u : ((uint32_t)quant_s4(xv, bscale, brinv) & 0xfu);
-      nw[e >> 3] |= nib << (4 * (e & 7));
+      const int code = is_tail ? 0 : quant_s4(xv, bscale, brinv);
+      nw[e >> 3] |= ((uint32_t)code & 0xfu) << (4 * (e & 7));
+      if (p.a_q8) {
+        // even elements of each 8-group first, then the odd ones: the order in which the GEMM's
+        // widening of the packed INT4 weights lays out K
+        const int i = fbase + eoff(e);
+        q8_s[(i & ~7) + ((i & 7) >> 1) + ((i & 1) << 2)] = (int8_t)code;
+      }
       if (p.x_rot) p.x_rot[(size_t)m * K + fbase + eoff(e)] = (uint16_t)vb;
     }
     // nibbles of index pairs (2i, 2i+1) sit in adjacent lanes: exchange and form bytes
@@ -442,9 +450,16 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
 
     // ---- coalesced copy-out
     {
-      uint4* dst = reinterpret_cast<uint4*>(p.a_pack + (size_t)m * (K / 2));
-      const uint4* src = reinterpret_cast<const uint4*>(pack_s);
-      for (int i = tid; i < K / 32; i += NT) dst[i] = src[i];
+      if (p.a_pack) {
+        uint4* dst = reinterpret_cast<uint4*>(p.a_pack + (size_t)m * (K / 2));
+        const uint4* src = reinterpret_cast<const uint4*>(pack_s);
+        for (int i = tid; i < K / 32; i += NT) dst[i] = src[i];
+      }
+      if (p.a_q8) {
+        uint4* dst = reinterpret_cast<uint4*>(p.a_q8 + (size_t)m * K);
+        const uint4* src = reinterpret_cast<const uint4*>(q8_s);
+        for (int i = tid; i < K / 16; i += NT) dst[i] = src[i];
+      }
       const size_t rb = (size_t)m * R, rl = (size_t)m * p.tail_ld;
       for (int r = tid; r < R; r += NT) {
         const uint16_t ix = st_idx[r];
@@ -524,12 +539,12 @@ float had_scale(int kind, int K) {
 }  // namespace
 
 int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float eps, int scale_mode,
-                 uint8_t* a_pack, float* body_scale, float* top_scale, uint16_t* tail_idx16,
+                 uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale, uint16_t* tail_idx16,
                  void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q, void* x_rot, cudaStream_t st) {
   if ((tail_idx16 || tail_val) && tail_ld < R) return TQ_ERR_BAD_ARG;
-  if (!x || !a_pack || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
+  if (!x || (!a_pack && !a_q8) || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
   if (dr < 1 || dr > K) return TQ_ERR_BAD_ARG;
-  if (!aligned16(x) || !aligned16(a_pack)) return TQ_ERR_MISALIGNED;
+  if (!aligned16(x) || (a_pack && !aligned16(a_pack)) || (a_q8 && !aligned16(a_q8))) return TQ_ERR_MISALIGNED;
   if (M == 0) return TQ_OK;
   PrologueParams p;
   p.x = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -541,6 +556,7 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
   p.hscale = had_scale(had_kind, K);
   p.scale_mode = scale_mode;
   p.a_pack = a_pack;
+  p.a_q8 = a_q8;
   p.body_scale = body_scale;
   p.top_scale = top_scale;
   p.tail_idx16 = tail_idx16;
@@ -554,10 +570,10 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
 }  // namespace tq
 
 extern "C" int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank,
-                                 float eps, uint8_t* a_pack, float* body_scale, float* top_scale,
+                                 float eps, uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale,
                                  uint16_t* tail_idx16, void* tail_val, int tail_ld, int32_t* idx32,
                                  int8_t* top_q, void* x_rot, void* stream) {
-  return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, body_scale, top_scale,
+  return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, a_q8, body_scale, top_scale,
                           tail_idx16, tail_val, tail_ld, idx32, top_q, x_rot, (cudaStream_t)stream);
 }
 
@@ -566,6 +582,6 @@ extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int d
                             int32_t* idx, float eps, void* stream) {
   if (dtype != TQ_BF16) return TQ_ERR_UNSUPPORTED;
   if (R > 0 && (!top_q || !idx || !top_scale)) return TQ_ERR_BAD_ARG;
-  return tq::run_prologue(A, M, K, TQ_HAD_NONE, R, descending_rank, eps, 0, A_pack, body_scale, top_scale,
+  return tq::run_prologue(A, M, K, TQ_HAD_NONE, R, descending_rank, eps, 0, A_pack, nullptr, body_scale, top_scale,
                           nullptr, nullptr, 0, idx, top_q, nullptr, (cudaStream_t)stream);
 }

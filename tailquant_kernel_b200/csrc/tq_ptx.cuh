@@ -77,10 +77,58 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+
+// K-major operand tile, rows of 128 bytes, 8-row groups 1024 bytes apart, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);   // start address
+  d |= (uint64_t)0 << 16;                     // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024u >> 4) << 32;          // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                     // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma, M = 128, both operands K-major.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc_i8() {
+  return (2u << 4)                    // D = S32
+         | (1u << 7) | (1u << 10)     // A, B = signed 8-bit
+         | ((uint32_t)(BN >> 3) << 17)
+         | ((uint32_t)(128 >> 4) << 24);
+}
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc_bf16() {
+  return (1u << 4)                    // D = F32
+         | (1u << 7) | (1u << 10)     // A, B = BF16
+         | ((uint32_t)(BN >> 3) << 17)
+         | ((uint32_t)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 
 // ------------------------------------------------------------------------------ host: tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -100,9 +148,11 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // Row-major 2-D tensor [outer, inner] of `esize`-byte elements with a row pitch of `pitch_bytes`,
-// un-swizzled box [box_outer, box_inner]; out-of-range parts of a box read as zero.
+// box [box_outer, box_inner], optionally written with the 128-byte swizzle (box_inner * esize must then
+// be 128 bytes); out-of-range parts of a box read as zero.
 inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* ptr,
-                               uint64_t inner, uint64_t outer, uint64_t pitch_bytes, int box_inner, int box_outer) {
+                               uint64_t inner, uint64_t outer, uint64_t pitch_bytes, int box_inner, int box_outer,
+                               bool swizzle128 = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
@@ -111,7 +161,8 @@ inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int esi
   cuuint32_t estr[2] = {1, 1};
   (void)esize;
   CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 

@@ -19,16 +19,17 @@ from . import ops
 
 
 class _Workspace:
-    def __init__(self, M: int, K: int, N: int, R: int, device):
+    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool):
         ld = (R + 7) // 8 * 8
         self.pro = ops.PrologueOut(
-            a_pack=torch.empty((M, K // 2), dtype=torch.uint8, device=device),
+            a_pack=None if mma else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
+            a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if mma else None,
             body_scale=torch.empty(M, dtype=torch.float32, device=device),
             top_scale=torch.empty(M, dtype=torch.float32, device=device),
             tail_idx=torch.zeros((M, ld), dtype=torch.int16, device=device) if R else None,
             tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=device) if R else None,
             R=R)
-        self.tail = torch.empty((M, N), dtype=torch.float32, device=device) if R else None
+        self.tail = torch.empty((M, N), dtype=torch.float32, device=device) if (R and not mma) else None
         self.acc = None  # int32 [M, N], split-K path only
         self.out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
 
@@ -38,22 +39,32 @@ class SplitLinear:
 
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, ratio: float = 0.05,
                  activation_percentile: float = 100.0, had_kind: Optional[int] = None, small_m: int = 64,
-                 split_k: int = 0):
+                 split_k: int = 0, tail_engine: str = "mma"):
+        """tail_engine: "mma" = tail on the tensor cores inside the GEMM kernel (default, fastest at
+        ratios of a few percent); "gather" = exact-order fp32 fma chain on the CUDA cores (bit-exact
+        against the CPU oracle, and the engine of the small-M path)."""
+        if tail_engine not in ("mma", "gather"):
+            raise RuntimeError("tail_engine must be 'mma' or 'gather'")
+        self.tail_engine = tail_engine
         if not weight.is_cuda:
             raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
         self.N, self.K = int(weight.shape[0]), int(weight.shape[1])
         self.ratio = float(ratio)
         self.R = ops.ceil_ratio_count(self.K, self.ratio)
         _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
-        self.w = ops.prepare_weight(weight, had_kind, t16=self.R > 0, bias=bias)
+        self.w = ops.prepare_weight(weight, had_kind, t16=self.R > 0, keep_w_rot=self.R > 0 and tail_engine == "mma",
+                                    bias=bias)
         self.small_m = int(small_m)
         self.split_k = int(split_k)
         self._ws: Dict[int, _Workspace] = {}
 
+    def _use_mma(self, M: int) -> bool:
+        return self.tail_engine == "mma" and M > self.small_m
+
     def workspace(self, M: int) -> _Workspace:
         ws = self._ws.get(M)
         if ws is None:
-            ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device)
+            ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M))
         return ws
 
     def _pick_split_k(self, M: int) -> int:
@@ -75,6 +86,9 @@ class SplitLinear:
         reference shares one prepare between q/k/v and gate/up:
         tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:124-134)."""
         w, pro = self.w, ws.pro
+        if self._use_mma(M):
+            return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot,
+                                      tail_idx=pro.tail_idx, tail_val=pro.tail_val, R=self.R, bias=w.bias)
         if self.R:
             ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
         if M <= self.small_m:

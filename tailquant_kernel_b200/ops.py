@@ -92,7 +92,7 @@ def default_had_kind(K: int) -> int:
 # --------------------------------------------------------------------------- prologue
 @dataclass
 class PrologueOut:
-    a_pack: torch.Tensor                 # [M, K/2] u8
+    a_pack: Optional[torch.Tensor]       # [M, K/2] u8
     body_scale: torch.Tensor             # [M] f32
     top_scale: torch.Tensor              # [M] f32
     tail_idx: Optional[torch.Tensor]     # [M, ld] int16 storage of u16 indices (first R valid)
@@ -101,11 +101,12 @@ class PrologueOut:
     idx32: Optional[torch.Tensor] = None  # [M, R] i32   (T4)
     top_q: Optional[torch.Tensor] = None  # [M, R] i8    (T4)
     x_rot: Optional[torch.Tensor] = None  # [M, K] bf16
+    a_q8: Optional[torch.Tensor] = None   # [M, K] i8, operand order of split_gemm_mma
 
 
 def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
                    eps: float = EPS, t16: bool = True, t4: bool = False, want_x_rot: bool = False,
-                   out: Optional[PrologueOut] = None) -> PrologueOut:
+                   want_q8: bool = False, want_pack: bool = True, out: Optional[PrologueOut] = None) -> PrologueOut:
     """Rotation + per-token INT4 + top-R tail split of x [M,K] bf16 in one kernel."""
     _check_cuda(x, "x", torch.bfloat16)
     _check(x.dim() == 2, "x must be [M, K]")
@@ -116,19 +117,20 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
         dev = x.device
         ld = (R + 7) // 8 * 8
         out = PrologueOut(
-            a_pack=torch.empty((M, K // 2), dtype=torch.uint8, device=dev),
+            a_pack=torch.empty((M, K // 2), dtype=torch.uint8, device=dev) if want_pack else None,
             body_scale=torch.empty(M, dtype=torch.float32, device=dev),
             top_scale=torch.empty(M, dtype=torch.float32, device=dev),
             tail_idx=torch.zeros((M, ld), dtype=torch.int16, device=dev) if (t16 and R) else None,
             tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=dev) if (t16 and R) else None,
             R=R,
+            a_q8=torch.empty((M, K), dtype=torch.int8, device=dev) if want_q8 else None,
             idx32=torch.empty((M, R), dtype=torch.int32, device=dev) if (t4 and R) else None,
             top_q=torch.empty((M, R), dtype=torch.int8, device=dev) if (t4 and R) else None,
             x_rot=torch.empty((M, K), dtype=torch.bfloat16, device=dev) if want_x_rot else None,
         )
     ld = out.tail_idx.shape[1] if out.tail_idx is not None else 0
     rc = _lib.load().tq_split_prologue(
-        _ptr(x), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack), _ptr(out.body_scale),
+        _ptr(x), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack), _ptr(out.a_q8), _ptr(out.body_scale),
         _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld, _ptr(out.idx32), _ptr(out.top_q),
         _ptr(out.x_rot), _stream())
     _lib.check(rc, f"split_prologue(M={M}, K={K}, had_kind={had_kind}, R={R})")
@@ -191,7 +193,7 @@ def prepare_weight(W: torch.Tensor, had_kind: Optional[int] = None, eps: float =
     dev = Wb.device
     b_col = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
     w_scale = torch.empty(N, dtype=torch.float32, device=dev)
-    need_rot = t16 or keep_w_rot
+    need_rot = bool(t16 or keep_w_rot)
     w_rot = torch.empty((N, K), dtype=torch.bfloat16, device=dev) if need_rot else None
     w_t = torch.empty((K, N), dtype=torch.bfloat16, device=dev) if t16 else None
     b_row = torch.empty((K, N // 2), dtype=torch.uint8, device=dev) if t4 else None
@@ -253,6 +255,36 @@ def split_gemm_fused(A_pack, body_scale, B_pack, w_scale, out, tail=None, bias=N
     rc = _lib.load().tq_split_gemm_fused(_ptr(A_pack), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale), _ptr(tail),
                                          _ptr(bias), _ptr(out), M, N, K, _stream())
     _lib.check(rc, f"split_gemm_fused(M={M}, N={N}, K={K})")
+    return out
+
+
+def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, tail_idx=None, tail_val=None, R: int = 0,
+                   bias=None, dbg_acc=None, dbg_tail=None):
+    """One kernel: dense INT4 x INT4 part on tcgen05 kind::i8 plus the tail as a bf16 tensor-core product
+    over the zero-filled tail matrix, fused dequant + bias, bf16 out."""
+    _check_cuda(a_q8, "a_q8", torch.int8)
+    _check_cuda(B_pack, "B_pack", torch.uint8)
+    _check_cuda(body_scale, "body_scale", torch.float32)
+    _check_cuda(w_scale, "w_scale", torch.float32)
+    _check_cuda(out, "out", torch.bfloat16)
+    M, K = a_q8.shape
+    N = B_pack.shape[0]
+    _check(B_pack.shape[1] * 2 == K, "a_q8 and B_pack disagree on K")
+    _check(out.numel() >= M * N, "out too small")
+    ld = 0
+    if R:
+        _check_cuda(w_rot, "w_rot", torch.bfloat16)
+        _check(tuple(w_rot.shape) == (N, K), "w_rot must be [N, K]")
+        _check_cuda(tail_idx, "tail_idx", torch.int16)
+        _check_cuda(tail_val, "tail_val", torch.bfloat16)
+        ld = tail_idx.shape[1]
+    if bias is not None:
+        _check_cuda(bias, "bias", torch.float32)
+    rc = _lib.load().tq_split_gemm_mma(_ptr(a_q8), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale),
+                                       _ptr(w_rot) if R else None, _ptr(tail_idx) if R else None,
+                                       _ptr(tail_val) if R else None, ld, int(R), _ptr(bias), _ptr(out),
+                                       _ptr(dbg_acc), _ptr(dbg_tail), M, N, K, _stream())
+    _lib.check(rc, f"split_gemm_mma(M={M}, N={N}, K={K}, R={R})")
     return out
 
 

@@ -232,14 +232,87 @@ def test_tail_gather_bit_exact(M, N, K, R):
     assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
 
 
-def _output_bounds(y_bits, y32):
+def _output_bounds(y_bits, y32, slack=0.0):
+    """max-abs <= 2e-2 (or half an output ulp where that is larger, plus `slack` for a tail that was
+    accumulated in another order) and mean-rel <= 1e-2 against the fp32 evaluation."""
     got = O.bf16_bits_to_f32(y_bits)
     err = np.abs(got.astype(np.float64) - y32.astype(np.float64))
     half_ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(y32), 1e-30))) - 8)
-    assert np.all(err <= np.maximum(2e-2, half_ulp) * (1 + 1e-6))
+    assert np.all(err <= np.maximum(2e-2, half_ulp * (1 + 1e-6) + slack))
     assert err.sum() / np.abs(y32).sum() <= 1e-2
 
 
+def permute_q8(codes):
+    """INT8 operand order of the fused GEMM: even elements of each 8-group, then the odd ones."""
+    M, K = codes.shape
+    g = codes.reshape(M, K // 8, 8)
+    return np.ascontiguousarray(np.concatenate((g[:, :, 0::2], g[:, :, 1::2]), axis=2).reshape(M, K))
+
+
+@pytest.mark.parametrize("kind,K,M,R", [(O.HAD_WHT, 1024, 9, 52), (O.HAD_WHT, 4096, 40, 205), (O.HAD_KRON12, 12288, 6, 615),
+                                        (O.HAD_BLOCK128, 14336, 5, 717), (O.HAD_WHT, 4096, 7, 0)])
+def test_prologue_int8_operand(kind, K, M, R):
+    xb = make_x(M, K, seed=3)
+    ref = O.prologue(xb, kind, R)
+    out = ops.split_prologue(dev_bf16(xb), kind, R, want_q8=True, want_pack=False)
+    assert out.a_pack is None
+    assert np.array_equal(out.a_q8.cpu().numpy(), permute_q8(ref.codes))
+    assert np.array_equal(out.body_scale.cpu().numpy(), ref.body_scale)
+    both = ops.split_prologue(dev_bf16(xb), kind, R, want_q8=True)
+    assert np.array_equal(both.a_pack.cpu().numpy(), ref.a_pack)
+    assert np.array_equal(both.a_q8.cpu().numpy(), permute_q8(ref.codes))
+
+
+@pytest.mark.parametrize("M,N,K,R,bias", [(100, 264, 512, 26, True), (256, 512, 1024, 0, False),
+                                          (300, 1032, 4096, 205, False), (129, 136, 12288, 615, True),
+                                          (2048, 512, 256, 13, False), (1, 8, 128, 3, False)])
+def test_split_gemm_mma(M, N, K, R, bias):
+    """Fused kernel: int32 accumulators bit-exact, tensor-core tail within fp32 accumulation error of the
+    fixed-order chain, bf16 output within the stated bounds."""
+    rng = np.random.default_rng(M + N + K + R)
+    qa, qw = rand_codes(rng, M, K), rand_codes(rng, N, K)
+    sx = rng.uniform(0.001, 0.02, M).astype(np.float32)
+    sw = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    b = rng.standard_normal(N, dtype=np.float32) if bias else None
+    w_rot = O.make_weights(N, K, seed=5)
+    acc = O.int_gemm(qa, qw)
+    y = O.dequant(acc, sx, sw)
+    ld = (R + 7) // 8 * 8
+    ti = np.zeros((M, max(ld, 8)), np.uint16)
+    tv = np.zeros((M, max(ld, 8)), np.uint16)
+    if R:
+        idx = np.sort(np.argsort(rng.random((M, K)), axis=1)[:, :R], axis=1).astype(np.int32)
+        val = O.f32_to_bf16_bits(rng.standard_normal((M, R), dtype=np.float32) * 3)
+        for r_ in range(M):  # tail positions carry code 0 in the dense operand, as the prologue guarantees
+            qa[r_, idx[r_]] = 0
+        acc = O.int_gemm(qa, qw)
+        y = O.dequant(acc, sx, sw)
+        tail = O.tail_t16(idx, val, w_rot)
+        y = (y + tail).astype(np.float32)
+        ti[:, :R] = idx
+        tv[:, :R] = val
+    if bias:
+        y = (y + b.reshape(1, -1)).astype(np.float32)
+    g = lambda a: torch.from_numpy(a).cuda()
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    dacc = torch.empty((M, N), dtype=torch.int32, device="cuda")
+    dtail = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    ops.split_gemm_mma(g(permute_q8(qa)), g(sx), g(O.pack_s4(qw)), g(sw), out, w_rot=dev_bf16(w_rot),
+                       tail_idx=g(ti.view(np.int16)), tail_val=dev_bf16(tv), R=R, bias=None if b is None else g(b),
+                       dbg_acc=dacc, dbg_tail=dtail)
+    assert np.array_equal(dacc.cpu().numpy(), acc), "int32 accumulators"
+    slack = 0.0
+    if R:
+        got_tail = dtail.cpu().numpy()
+        scale = np.abs(O.bf16_bits_to_f32(val)).max() * np.abs(O.bf16_bits_to_f32(w_rot)).max() * R
+        assert np.abs(got_tail - tail).max() <= 1e-5 * scale, "tensor-core tail vs fixed-order fp32 chain"
+        slack = 1e-5 * scale
+    _output_bounds(host_bits(out), y, slack=slack)
+    if not R:
+        assert np.array_equal(host_bits(out), O.f32_to_bf16_bits(y))
+
+
+@pytest.mark.parametrize("engine", ["gather", "mma"])
 @pytest.mark.parametrize("M,K,N,kind,ratio,bias", [(200, 1024, 264, O.HAD_WHT, 0.05, True),
                                                    (512, 4096, 4096, O.HAD_WHT, 0.05, False),
                                                    (64, 4096, 512, O.HAD_WHT, 0.05, False),
@@ -248,23 +321,34 @@ def _output_bounds(y_bits, y32):
                                                    (140, 12288, 256, O.HAD_KRON12, 0.05, False),
                                                    (130, 14336, 128, O.HAD_BLOCK128, 0.10, False),
                                                    (150, 4096, 136, O.HAD_WHT, 0.0, False)])
-def test_split_linear_end_to_end(M, K, N, kind, ratio, bias):
+def test_split_linear_end_to_end(M, K, N, kind, ratio, bias, engine):
     """Config 1 of the baseline (M=512, K=N=4096, 16 outlier channels x50, ratio 0.05) and smaller /
-    ragged relatives, through the host-side SplitLinear object."""
+    ragged relatives, through the host-side SplitLinear object.  The gather engine must reproduce the
+    oracle's bf16 bits; the tensor-core tail engine must stay within the stated output bounds (its tail sum
+    is an fp32 tensor-core accumulation, not the fixed-order chain) and agree with the gather engine on
+    all but a small fraction of outputs, each off by one bf16 ulp."""
     from tailquant_kernel_b200 import SplitLinear
     xb = O.make_activations(M, K, seed=0, n_outlier=16)
     wb = O.make_weights(N, K, seed=1)
     b = np.random.default_rng(2).standard_normal(N, dtype=np.float32) if bias else None
     R = O.ceil_ratio_count(K, ratio)
     yb_ref, y32, p, acc = O.split_linear_t16(xb, O.prepare_weight(wb, kind), kind, R, bias=b)
-    lin = SplitLinear(dev_bf16(wb), None if b is None else torch.from_numpy(b).cuda(), ratio=ratio, had_kind=kind)
+    lin = SplitLinear(dev_bf16(wb), None if b is None else torch.from_numpy(b).cuda(), ratio=ratio, had_kind=kind,
+                      tail_engine=engine)
     y = lin(dev_bf16(xb))
     torch.cuda.synchronize()
     yb = host_bits(y)
-    assert np.array_equal(yb, yb_ref), f"{(yb != yb_ref).sum()} of {yb.size} bf16 outputs differ"
-    _output_bounds(yb, y32)
+    if engine == "gather" or R == 0 or M <= lin.small_m:
+        assert np.array_equal(yb, yb_ref), f"{(yb != yb_ref).sum()} of {yb.size} bf16 outputs differ"
+        _output_bounds(yb, y32)
+    else:
+        _output_bounds(yb, y32, slack=1e-3)
+        diff = yb != yb_ref
+        assert diff.mean() < 0.01, f"{diff.mean():.4f} of the outputs differ from the fixed-order result"
+        ulp = np.abs(yb.astype(np.int32) - yb_ref.astype(np.int32))[diff]
+        assert ulp.size == 0 or ulp.max() <= 1 or np.all((ulp <= 1) | (np.abs(y32[diff]) < 1e-2))
     y2 = lin(dev_bf16(xb))  # second call reuses the workspaces
-    assert np.array_equal(host_bits(y2), yb_ref)
+    assert np.array_equal(host_bits(y2), yb)
 
 
 def test_t4_reference_epilogues():
