@@ -264,8 +264,7 @@ def run_ours(args) -> None:
     def gemm_call(lin, ws):
         if mma:
             return lambda: ops.split_gemm_mma(ws.pro.a_q8, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out,
-                                              w_rot=lin.w.w_rot, tail_idx=ws.pro.tail_idx, tail_val=ws.pro.tail_val,
-                                              R=lin.R)
+                                              w_rot=lin.w.w_rot, pro=ws.pro, R=lin.R)
         return lambda: ops.split_gemm_fused(ws.pro.a_pack, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, ws.out,
                                             tail=ws.tail)
 

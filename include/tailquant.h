@@ -31,8 +31,12 @@ extern "C" {
 /* Rotation applied to the last dimension before quantisation. */
 #define TQ_HAD_NONE 0     /* input is already rotated                                       */
 #define TQ_HAD_WHT 1      /* K = 2^n, 512..8192 : normalised Walsh-Hadamard                 */
-#define TQ_HAD_KRON12 2   /* K = 12*2^n (3072, 12288): (H12 (x) H_2^n)/sqrt(K), H12 = Paley */
+#define TQ_HAD_KRON12 2   /* K = 12*2^n (6144, 12288): (H12 (x) H_2^n)/sqrt(K), H12 = Paley */
 #define TQ_HAD_BLOCK128 3 /* K % 2048 == 0 (e.g. 14336): block-diagonal H128/sqrt(128)      */
+
+/* Entries per (row, 128-wide K slice) held by the tail records; longer runs are completed from the
+ * sorted lists. */
+#define TQ_TAIL_REC_CAP 16
 
 /* 16-bit float formats of activation inputs / outputs. */
 #define TQ_BF16 0
@@ -65,14 +69,21 @@ const char* tq_last_cuda_error(void);
  *   tail_idx16   [M,tail_ld] u16 ascending channel indices, R per row (tail mode T16; may be NULL)
  *   tail_val     [M,tail_ld] bf16 rotated values at those indices    (T16; may be NULL)
  *   tail_ld      row pitch (elements) of tail_idx16 / tail_val, >= R; idx32 / top_q are dense [M,R]
+ *   tail_ptr     [M,ptr_ld] u16, ptr_ld >= K/128 + 1: tail_ptr[m][j] = number of tail entries of row m
+ *                with index < 128 j (run boundaries for tq_split_gemm_mma; K % 128 == 0; may be NULL)
+ *   tail_rec     [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
+ *                tile and 128-wide K slice as (index & 127) | bf16 bits << 16, entry j of the 128 rows
+ *                contiguous -- what tq_split_gemm_mma reads, one coalesced load per j (may be NULL)
+ *   tail_cnt     [ceil(M/128)][K/128][128] u16 entries per (row, slice) (with tail_rec)
  *   idx32        [M,R] i32 the same indices                          (T4; may be NULL)
  *   top_q        [M,R] i8  clamp(rint(x / top_scale), -8, 7)         (T4; may be NULL)
  *   x_rot        [M,K] bf16 rotated activations                      (debug / weight prep; may be NULL)
  */
 int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank, float eps,
                       uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale,
-                      uint16_t* tail_idx16, void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q,
-                      void* x_rot, void* stream);
+                      uint16_t* tail_idx16, void* tail_val, int tail_ld, uint16_t* tail_ptr, int ptr_ld,
+                      uint32_t* tail_rec, uint16_t* tail_cnt, int32_t* idx32, int8_t* top_q, void* x_rot,
+                      void* stream);
 
 /* Reference-signature select+pack on an already rotated matrix (T4 outputs):
  * fused_topr_pack(A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps)
@@ -134,10 +145,13 @@ int tq_split_gemm_fused(const uint8_t* a_pack, const float* body_scale, const ui
  * can differ from that path in the last bit.  Has the role of the reference's fused-epilogue
  * prototypes (tools/quarot_split_fused_epilogue_ext_v1.py:283-432).
  *   a_q8      [M,K] i8 from tq_split_prologue       w_rot  [N,K] bf16 from tq_prepare_weight (R > 0)
+ *   tail_ptr, tail_rec, tail_cnt  from tq_split_prologue (R > 0)
  *   dbg_acc   optional [M,N] i32: accumulators      dbg_tail  optional [M,N] f32: tail sums */
 int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                       const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
-                      const void* tail_val, int tail_ld, int R, const float* bias, void* out_bf16,
+                      const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
+                      const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
+                      const float* bias, void* out_bf16,
                       int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream);
 
 /* Finisher of the split-K path: out = bf16((float(C)*body_scale[m])*w_scale[n] + tail + bias). */

@@ -109,10 +109,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
     for (int s = 0; s < S::SP; ++s) {
       mbar_init(full_p(s), 1);
-      mbar_init(empty_p(s), NUT);
+      mbar_init(empty_p(s), NUM_UNPACK_WARPS);
     }
     for (int s = 0; s < S::SU; ++s) {
-      mbar_init(full_u(s), NUT);
+      mbar_init(full_u(s), NUM_UNPACK_WARPS);
       mbar_init(empty_u(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -295,8 +295,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(full_u(su));
-        mbar_arrive(empty_p(sp));
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(full_u(su));
+          mbar_arrive(empty_p(sp));
+        }
         if (++sp == S::SP) {
           sp = 0;
           php ^= 1u;

@@ -42,10 +42,13 @@ constexpr int G_THREADS = (6 + G_BUILD_WARPS) * 32;
 constexpr int G_SENT = 0x7fffffff;
 
 struct SplitGemmParams {
-  int M, N, K, R, ld;
+  int M, N, K, R, ld, ptr_ld;
   int tiles_m, tiles_n, kb_total, has_tail;
-  const uint16_t* idx;
-  const uint16_t* val;
+  const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
+  const uint16_t* val;   // [M, ld] tail values
+  const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
+  const uint32_t* rec;   // [tiles_m][K/128][TQ_TAIL_REC_CAP][128]: (index & 127) | bf16 << 16
+  const uint16_t* cnt;   // [tiles_m][K/128][128]: entries of the row in the slice
   const float* sx;
   const float* sw;
   const float* bias;
@@ -98,10 +101,10 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     for (int s = 0; s < S::SP; ++s) {
       mbar_init(full_p(s), 1);
-      mbar_init(empty_p(s), G_NBT);
+      mbar_init(empty_p(s), G_BUILD_WARPS / 2);
     }
     for (int s = 0; s < S::SU; ++s) {
-      mbar_init(full_u(s), G_NBT + 1);  // every builder thread + the producer's expect_tx arrival
+      mbar_init(full_u(s), G_BUILD_WARPS / 2 + 1);  // four builder warps + the producer's expect_tx arrival
       mbar_init(empty_u(s), 1);
     }
     mbar_init(acc_full, 1);
@@ -274,82 +277,142 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------------ builders
+    // Two groups of four warps.  With a tail, group 0 widens the INT4 weight tiles and group 1 builds the
+    // bf16 tail tiles, so neither waits for the other's slots; without one, the groups take alternate
+    // K slices of the widening.
     const int btid = threadIdx.x - 6 * 32;
-    const int half = btid >> 7, brow = btid & 127;  // tail tiles: one thread per row and 64-wide half
-    int q = 0, sp = 0;
-    uint32_t php = 0;
+    const int grp = btid >> 7, gtid = btid & 127;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-      const int mt = t % p.tiles_m;
-      const int grow = mt * G_BM + brow;
-      const uint16_t* irow = p.idx + (size_t)grow * p.ld;
-      const uint16_t* vrow = p.val + (size_t)grow * p.ld;
-      int cur = 0, kk = G_SENT;
-      uint32_t xx = 0;
-      if (has_tail && grow < p.M && p.R > 0) {
-        kk = (int)__ldg(irow);
-        xx = (uint32_t)__ldg(vrow);
+
+    // INT4 -> INT8 (x16) of one weight tile: staging buffer (kbg mod SP) -> B region of slot use q
+    auto widen = [&](int q, int kbg) -> bool {
+      const int s = slot_of(q), sp = kbg % S::SP;
+      const uint32_t php = (uint32_t)((kbg / S::SP) & 1);
+      if (!mbar_wait(full_p(sp), php, abort_flag, 0x80000u)) return false;
+      if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u)) return false;
+      tc_fence_after();
+      const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
+      unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
+#pragma unroll
+      for (int task = gtid; task < BN * 4; task += 128) {
+        const int row = task >> 2, piece = task & 3;
+        const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
+        unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
+        uint4 lo, hi;
+        lo.x = (w.x << 4) & 0xf0f0f0f0u;
+        lo.y = w.x & 0xf0f0f0f0u;
+        lo.z = (w.y << 4) & 0xf0f0f0f0u;
+        lo.w = w.y & 0xf0f0f0f0u;
+        hi.x = (w.z << 4) & 0xf0f0f0f0u;
+        hi.y = w.z & 0xf0f0f0f0u;
+        hi.z = (w.w << 4) & 0xf0f0f0f0u;
+        hi.w = w.w & 0xf0f0f0f0u;
+        *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
       }
-      for (int kb = 0; kb < p.kb_total; ++kb) {
-        {  // INT4 -> INT8 (x16) of the weight tile
-          const int s = slot_of(q);
-          if (!(ok = mbar_wait(full_p(sp), php, abort_flag, 0x80000u))) break;
-          if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u))) break;
-          tc_fence_after();
-          const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
-          unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
-#pragma unroll
-          for (int task = btid; task < BN * 4; task += G_NBT) {
-            const int row = task >> 2, piece = task & 3;
-            const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
-            unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
-            uint4 lo, hi;
-            lo.x = (w.x << 4) & 0xf0f0f0f0u;
-            lo.y = w.x & 0xf0f0f0f0u;
-            lo.z = (w.y << 4) & 0xf0f0f0f0u;
-            lo.w = w.y & 0xf0f0f0f0u;
-            hi.x = (w.z << 4) & 0xf0f0f0f0u;
-            hi.y = w.z & 0xf0f0f0f0u;
-            hi.z = (w.w << 4) & 0xf0f0f0f0u;
-            hi.w = w.w & 0xf0f0f0f0u;
-            *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
-            *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(full_u(s));
+        mbar_arrive(empty_p(sp));
+      }
+      return true;
+    };
+
+    if (!has_tail || grp == 0) {
+      int q = 0, kbg = 0;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        for (int kb = 0; kb < p.kb_total && ok; ++kb, ++kbg) {
+          if (has_tail) {
+            ok = widen(q, kbg);
+            q += 3;
+          } else {
+            if ((kbg & 1) == grp) ok = widen(q, kbg);
+            q += 1;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive(full_u(s));
-          mbar_arrive(empty_p(sp));
-          if (++sp == S::SP) {
-            sp = 0;
-            php ^= 1u;
-          }
-          ++q;
         }
-        if (has_tail) {  // zero-filled bf16 tail tiles of the two 64-wide halves of this K slice
-          const int sa = slot_of(q), sb = slot_of(q + 1);
-          if (!(ok = mbar_wait(empty_u(sa), par_of(q) ^ 1u, abort_flag, 0x200000u))) break;
-          if (!(ok = mbar_wait(empty_u(sb), par_of(q + 1) ^ 1u, abort_flag, 0x400000u))) break;
-          tc_fence_after();
-          unsigned char* arow = sm + (half ? sb : sa) * S::SLOT + (brow >> 3) * 1024 + (brow & 7) * 128;
-          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      }
+    } else {
+      // bf16 tail tiles: one thread per row.  The row's entries of a 128-wide K slice come as one record
+      // column ([slice][j][row], so a warp reads 128 contiguous bytes per j), fetched two slices ahead.
+      constexpr int C = TQ_TAIL_REC_CAP;
+      const int brow = gtid;
+      const uint32_t roff = (uint32_t)((brow >> 3) * 1024 + (brow & 7) * 128);
+      int q = 1;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const int mt = t % p.tiles_m;
+        const int grow = mt * G_BM + brow;
+        const uint32_t* recb = p.rec + (size_t)mt * p.kb_total * C * 128 + brow;
+        const uint16_t* cntb = p.cnt + (size_t)mt * p.kb_total * 128 + brow;
+        auto fetch = [&](uint32_t(&r)[C], int& n, int kb) {
+          if (kb < p.kb_total) {
+            // volatile asm keeps these loads where they are written: ahead of the barrier waits of the
+            // slices in between, so their latency is never on the path "slot free" -> "slot full"
+            uint32_t n16;
+            asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 128));
+            n = (int)n16;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + (c << 4)) = z;
-          const int kbase = kb * G_BK + half * 64;
-          while (kk < kbase + 64) {
-            if (kk >= kbase) {
-              const int c = kk - kbase;
-              *reinterpret_cast<uint16_t*>(arow + ((((c >> 3) ^ (brow & 7))) << 4) + (c & 7) * 2) = (uint16_t)xx;
-            }
-            if (++cur < p.R) {
-              kk = (int)__ldg(irow + cur);
-              xx = (uint32_t)__ldg(vrow + cur);
-            } else {
-              kk = G_SENT;
-            }
+            for (int j = 0; j < C; ++j)
+              asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + ((size_t)kb * C + j) * 128));
+          } else {
+            n = 0;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive(full_u(sa));
-          mbar_arrive(full_u(sb));
-          q += 2;
+          // the fetch after this one is pulled towards the SM now, so that when its loads are issued they
+          // return quickly: a proxy fence waits for the thread's outstanding loads, and those fences sit
+          // between "slot free" and "slot full"
+          if (kb + 2 < p.kb_total) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(cntb + (size_t)(kb + 2) * 128));
+#pragma unroll
+            for (int j = 0; j < C; ++j)
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(recb + ((size_t)(kb + 2) * C + j) * 128));
+          }
+        };
+        auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int s = slot_of(q + h);
+            if (!mbar_wait(empty_u(s), par_of(q + h) ^ 1u, abort_flag, 0x200000u)) return false;
+            tc_fence_after();
+            unsigned char* arow = sm + s * S::SLOT + roff;
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+              const int c = (int)(r[j] & 127u) - 64 * h;  // position inside this 64-wide half
+              if (j < n && c >= 0 && c < 64)
+                *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) = (uint16_t)(r[j] >> 16);
+            }
+            if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list
+              const size_t lrow = (size_t)grow;
+              const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+              for (int j = C; j < n; ++j) {
+                const int c = (int)__ldg(p.idx + lrow * p.ld + e0 + j) - kb * G_BK - 64 * h;
+                if (c >= 0 && c < 64)
+                  *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                      __ldg(p.val + lrow * p.ld + e0 + j);
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_u(s));
+          }
+          q += 3;
+          return true;
+        };
+        uint32_t ra[C], rb[C];
+        int na = 0, nb = 0;
+        fetch(ra, na, 0);
+        fetch(rb, nb, 1);
+        for (int kb = 0; kb < p.kb_total && ok; kb += 2) {
+          ok = fill(kb, ra, na);
+          if (!ok) break;
+          fetch(ra, na, kb + 2);
+          if (kb + 1 < p.kb_total) {
+            ok = fill(kb + 1, rb, nb);
+            if (!ok) break;
+            fetch(rb, nb, kb + 3);
+          }
         }
       }
     }
@@ -406,12 +469,16 @@ int launch_split_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_ro
 
 extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                                  const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
-                                 const void* tail_val, int tail_ld, int R, const float* bias, void* out_bf16,
+                                 const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
+                                 const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
+                                 void* out_bf16,
                                  int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream) {
   using namespace tq;
   if (!a_q8 || !body_scale || !b_col || !w_scale || !out_bf16 || M < 0 || N <= 0 || K <= 0 || R < 0 || R >= K)
     return TQ_ERR_BAD_ARG;
-  if (R > 0 && (!w_rot || !tail_idx16 || !tail_val || tail_ld < R)) return TQ_ERR_BAD_ARG;
+  if (R > 0 && (!w_rot || !tail_idx16 || !tail_val || tail_ld < R || !tail_ptr || ptr_ld < K / G_BK + 1 || !tail_rec ||
+                !tail_cnt))
+    return TQ_ERR_BAD_ARG;
   if (K % G_BK != 0 || N % 8 != 0 || K > 65536) return TQ_ERR_UNSUPPORTED;
   if (!aligned16(a_q8) || !aligned16(b_col) || !aligned16(out_bf16) || !aligned16(w_scale) ||
       (R > 0 && !aligned16(w_rot)) || (bias && !aligned16(bias)) || (dbg_acc && !aligned16(dbg_acc)) ||
@@ -424,6 +491,10 @@ extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, co
   p.K = K;
   p.R = R;
   p.ld = tail_ld;
+  p.ptr_ld = ptr_ld;
+  p.ptr = tail_ptr;
+  p.rec = tail_rec;
+  p.cnt = tail_cnt;
   p.has_tail = R > 0 ? 1 : 0;
   p.idx = tail_idx16;
   p.val = reinterpret_cast<const uint16_t*>(tail_val);

@@ -30,7 +30,7 @@ __device__ constexpr unsigned short H12_NEG[12] = {0x000, 0x475, 0x8e9, 0x1d3, 0
 
 struct PrologueParams {
   const __nv_bfloat16* x;
-  int M, R, dr, tail_ld;
+  int M, R, dr, tail_ld, ptr_ld;
   float eps, hscale;
   int scale_mode;  // 0: max(t, eps) / 7 (activations); 1: max(t / 7, eps) (weights)
   uint8_t* a_pack;
@@ -39,6 +39,9 @@ struct PrologueParams {
   float* top_scale;
   uint16_t* tail_idx16;
   uint16_t* tail_val;
+  uint16_t* tail_ptr;  // [M, ptr_ld]: entries with index < 128 * j, j = 0 .. K/128
+  uint32_t* tail_rec;  // [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128]: (index & 127) | bf16 << 16
+  uint16_t* tail_cnt;  // [ceil(M/128)][K/128][128]: entries per 128-wide slice
   int32_t* idx32;
   int8_t* top_q;
   uint16_t* x_rot;
@@ -388,6 +391,28 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
         run += loc[j];
       }
       __syncthreads();
+      if (p.tail_ptr) {  // run boundaries of the row's ascending index list at multiples of 128
+        for (int j = tid; j <= K / 128; j += NT) {
+          int cnt = R;
+          if (j < K / 128) {
+            const uint32_t pre = prefix[8 * j];
+            cnt = (int)(pre & 0xffffu) + min((int)(pre >> 16), R - cnt_lt);
+          }
+          p.tail_ptr[(size_t)m * p.ptr_ld + j] = (uint16_t)cnt;
+        }
+      }
+      if (p.tail_cnt) {
+        for (int j = tid; j < K / 128; j += NT) {
+          const uint32_t pa = prefix[8 * j];
+          const int ea = (int)(pa & 0xffffu) + min((int)(pa >> 16), R - cnt_lt);
+          int eb = R;
+          if (j + 1 < K / 128) {
+            const uint32_t pb = prefix[8 * (j + 1)];
+            eb = (int)(pb & 0xffffu) + min((int)(pb >> 16), R - cnt_lt);
+          }
+          p.tail_cnt[((size_t)(m >> 7) * (K / 128) + j) * 128 + (m & 127)] = (uint16_t)(eb - ea);
+        }
+      }
     }
 
     // ---- codes, tail entries
@@ -416,6 +441,13 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
             const int pos = ngt + min(neq, need);
             st_idx[pos] = (uint16_t)i;
             st_val[pos] = (uint16_t)vb;
+            if (p.tail_rec) {  // the entry's place in the record of its 128-wide slice
+              const uint32_t ps = prefix[(i >> 7) << 3];
+              const int j = pos - ((int)(ps & 0xffffu) + min((int)(ps >> 16), need));
+              if (j < TQ_TAIL_REC_CAP)
+                p.tail_rec[(((size_t)(m >> 7) * (K / 128) + (i >> 7)) * TQ_TAIL_REC_CAP + j) * 128 + (m & 127)] =
+                    (uint32_t)(i & 127) | (vb << 16);
+            }
             if (p.top_q) st_q[pos] = (int8_t)quant_s4(xv, tscale, trinv);
           }
         }
@@ -514,14 +546,14 @@ int dispatch(int kind, int K, const PrologueParams& p, cudaStream_t st) {
   TQ_CASE(TQ_HAD_WHT, 2048)
   TQ_CASE(TQ_HAD_WHT, 4096)
   TQ_CASE(TQ_HAD_WHT, 8192)
-  TQ_CASE(TQ_HAD_KRON12, 3072)
+  TQ_CASE(TQ_HAD_KRON12, 6144)
   TQ_CASE(TQ_HAD_KRON12, 12288)
   TQ_CASE(TQ_HAD_BLOCK128, 2048)
   TQ_CASE(TQ_HAD_BLOCK128, 14336)
   TQ_CASE(TQ_HAD_NONE, 512)
   TQ_CASE(TQ_HAD_NONE, 1024)
   TQ_CASE(TQ_HAD_NONE, 2048)
-  TQ_CASE(TQ_HAD_NONE, 3072)
+  TQ_CASE(TQ_HAD_NONE, 6144)
   TQ_CASE(TQ_HAD_NONE, 4096)
   TQ_CASE(TQ_HAD_NONE, 8192)
   TQ_CASE(TQ_HAD_NONE, 12288)
@@ -540,8 +572,11 @@ float had_scale(int kind, int K) {
 
 int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float eps, int scale_mode,
                  uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale, uint16_t* tail_idx16,
-                 void* tail_val, int tail_ld, int32_t* idx32, int8_t* top_q, void* x_rot, cudaStream_t st) {
+                 void* tail_val, int tail_ld, uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt,
+                 int32_t* idx32, int8_t* top_q, void* x_rot, cudaStream_t st) {
   if ((tail_idx16 || tail_val) && tail_ld < R) return TQ_ERR_BAD_ARG;
+  if (tail_ptr && (ptr_ld < K / 128 + 1 || K % 128 != 0)) return TQ_ERR_BAD_ARG;
+  if ((tail_rec != nullptr) != (tail_cnt != nullptr) || (tail_rec && K % 128 != 0)) return TQ_ERR_BAD_ARG;
   if (!x || (!a_pack && !a_q8) || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
   if (dr < 1 || dr > K) return TQ_ERR_BAD_ARG;
   if (!aligned16(x) || (a_pack && !aligned16(a_pack)) || (a_q8 && !aligned16(a_q8))) return TQ_ERR_MISALIGNED;
@@ -552,6 +587,10 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
   p.R = R;
   p.dr = dr;
   p.tail_ld = tail_ld;
+  p.ptr_ld = ptr_ld;
+  p.tail_ptr = tail_ptr;
+  p.tail_rec = tail_rec;
+  p.tail_cnt = tail_cnt;
   p.eps = eps;
   p.hscale = had_scale(had_kind, K);
   p.scale_mode = scale_mode;
@@ -571,10 +610,12 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
 
 extern "C" int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank,
                                  float eps, uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale,
-                                 uint16_t* tail_idx16, void* tail_val, int tail_ld, int32_t* idx32,
-                                 int8_t* top_q, void* x_rot, void* stream) {
+                                 uint16_t* tail_idx16, void* tail_val, int tail_ld, uint16_t* tail_ptr,
+                                 int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt, int32_t* idx32, int8_t* top_q,
+                                 void* x_rot, void* stream) {
   return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, a_q8, body_scale, top_scale,
-                          tail_idx16, tail_val, tail_ld, idx32, top_q, x_rot, (cudaStream_t)stream);
+                          tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld, tail_rec, tail_cnt, idx32, top_q, x_rot,
+                          (cudaStream_t)stream);
 }
 
 extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int descending_rank,
@@ -583,5 +624,5 @@ extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int d
   if (dtype != TQ_BF16) return TQ_ERR_UNSUPPORTED;
   if (R > 0 && (!top_q || !idx || !top_scale)) return TQ_ERR_BAD_ARG;
   return tq::run_prologue(A, M, K, TQ_HAD_NONE, R, descending_rank, eps, 0, A_pack, nullptr, body_scale, top_scale,
-                          nullptr, nullptr, 0, idx, top_q, nullptr, (cudaStream_t)stream);
+                          nullptr, nullptr, 0, nullptr, 0, nullptr, nullptr, idx, top_q, nullptr, (cudaStream_t)stream);
 }

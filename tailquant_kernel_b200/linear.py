@@ -24,6 +24,11 @@ class _Workspace:
         self.pro = ops.PrologueOut(
             a_pack=None if mma else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
             a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if mma else None,
+            tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=device) if (mma and R) else None,
+            tail_rec=torch.empty(((M + 127) // 128, K // 128, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
+            if (mma and R) else None,
+            tail_cnt=torch.zeros(((M + 127) // 128, K // 128, 128), dtype=torch.int16, device=device)
+            if (mma and R) else None,
             body_scale=torch.empty(M, dtype=torch.float32, device=device),
             top_scale=torch.empty(M, dtype=torch.float32, device=device),
             tail_idx=torch.zeros((M, ld), dtype=torch.int16, device=device) if R else None,
@@ -87,8 +92,8 @@ class SplitLinear:
         tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:124-134)."""
         w, pro = self.w, ws.pro
         if self._use_mma(M):
-            return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot,
-                                      tail_idx=pro.tail_idx, tail_val=pro.tail_val, R=self.R, bias=w.bias)
+            return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot, pro=pro,
+                                      R=self.R, bias=w.bias)
         if self.R:
             ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
         if M <= self.small_m:

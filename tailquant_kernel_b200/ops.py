@@ -28,6 +28,7 @@ from . import _lib
 from ._lib import TQ_BF16, TQ_FP16, TQ_HAD_BLOCK128, TQ_HAD_KRON12, TQ_HAD_NONE, TQ_HAD_WHT
 
 EPS = 1e-8
+TAIL_REC_CAP = 16  # TQ_TAIL_REC_CAP of include/tailquant.h
 
 
 # --------------------------------------------------------------------------- helpers
@@ -102,6 +103,9 @@ class PrologueOut:
     top_q: Optional[torch.Tensor] = None  # [M, R] i8    (T4)
     x_rot: Optional[torch.Tensor] = None  # [M, K] bf16
     a_q8: Optional[torch.Tensor] = None   # [M, K] i8, operand order of split_gemm_mma
+    tail_ptr: Optional[torch.Tensor] = None  # [M, K/128 + 1] int16 storage of u16 run boundaries
+    tail_rec: Optional[torch.Tensor] = None  # [ceil(M/128), K/128, 16, 128] int32: (index & 127) | bf16 << 16
+    tail_cnt: Optional[torch.Tensor] = None  # [ceil(M/128), K/128, 128] int16: entries per (row, slice)
 
 
 def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
@@ -124,15 +128,21 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
             tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=dev) if (t16 and R) else None,
             R=R,
             a_q8=torch.empty((M, K), dtype=torch.int8, device=dev) if want_q8 else None,
+            tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=dev) if (want_q8 and R) else None,
+            tail_rec=torch.empty(((M + 127) // 128, K // 128, TAIL_REC_CAP, 128), dtype=torch.int32, device=dev)
+            if (want_q8 and R) else None,
+            tail_cnt=torch.zeros(((M + 127) // 128, K // 128, 128), dtype=torch.int16, device=dev)
+            if (want_q8 and R) else None,
             idx32=torch.empty((M, R), dtype=torch.int32, device=dev) if (t4 and R) else None,
             top_q=torch.empty((M, R), dtype=torch.int8, device=dev) if (t4 and R) else None,
             x_rot=torch.empty((M, K), dtype=torch.bfloat16, device=dev) if want_x_rot else None,
         )
     ld = out.tail_idx.shape[1] if out.tail_idx is not None else 0
+    pld = out.tail_ptr.shape[1] if out.tail_ptr is not None else 0
     rc = _lib.load().tq_split_prologue(
         _ptr(x), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack), _ptr(out.a_q8), _ptr(out.body_scale),
-        _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld, _ptr(out.idx32), _ptr(out.top_q),
-        _ptr(out.x_rot), _stream())
+        _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld, _ptr(out.tail_ptr), pld, _ptr(out.tail_rec),
+        _ptr(out.tail_cnt), _ptr(out.idx32), _ptr(out.top_q), _ptr(out.x_rot), _stream())
     _lib.check(rc, f"split_prologue(M={M}, K={K}, had_kind={had_kind}, R={R})")
     return out
 
@@ -258,8 +268,8 @@ def split_gemm_fused(A_pack, body_scale, B_pack, w_scale, out, tail=None, bias=N
     return out
 
 
-def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, tail_idx=None, tail_val=None, R: int = 0,
-                   bias=None, dbg_acc=None, dbg_tail=None):
+def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Optional[PrologueOut] = None,
+                   R: int = 0, bias=None, dbg_acc=None, dbg_tail=None):
     """One kernel: dense INT4 x INT4 part on tcgen05 kind::i8 plus the tail as a bf16 tensor-core product
     over the zero-filled tail matrix, fused dequant + bias, bf16 out."""
     _check_cuda(a_q8, "a_q8", torch.int8)
@@ -275,14 +285,24 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, tail_idx=
     if R:
         _check_cuda(w_rot, "w_rot", torch.bfloat16)
         _check(tuple(w_rot.shape) == (N, K), "w_rot must be [N, K]")
+        _check(pro is not None, "the prologue outputs are needed when R > 0")
+        tail_idx, tail_val, tail_ptr, tail_rec, tail_cnt = pro.tail_idx, pro.tail_val, pro.tail_ptr, pro.tail_rec, pro.tail_cnt
         _check_cuda(tail_idx, "tail_idx", torch.int16)
         _check_cuda(tail_val, "tail_val", torch.bfloat16)
+        _check_cuda(tail_ptr, "tail_ptr", torch.int16)
+        _check_cuda(tail_rec, "tail_rec", torch.int32)
+        _check_cuda(tail_cnt, "tail_cnt", torch.int16)
+        _check(tail_ptr.shape[0] == M and tail_ptr.shape[1] >= K // 128 + 1, "tail_ptr must be [M, K/128 + 1]")
+        _check(tuple(tail_rec.shape) == ((M + 127) // 128, K // 128, TAIL_REC_CAP, 128), "tail_rec has the wrong shape")
+        _check(tuple(tail_cnt.shape) == ((M + 127) // 128, K // 128, 128), "tail_cnt has the wrong shape")
         ld = tail_idx.shape[1]
     if bias is not None:
         _check_cuda(bias, "bias", torch.float32)
     rc = _lib.load().tq_split_gemm_mma(_ptr(a_q8), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale),
                                        _ptr(w_rot) if R else None, _ptr(tail_idx) if R else None,
-                                       _ptr(tail_val) if R else None, ld, int(R), _ptr(bias), _ptr(out),
+                                       _ptr(tail_val) if R else None, ld, _ptr(tail_ptr) if R else None,
+                                       tail_ptr.shape[1] if R else 0, _ptr(tail_rec) if R else None,
+                                       _ptr(tail_cnt) if R else None, int(R), _ptr(bias), _ptr(out),
                                        _ptr(dbg_acc), _ptr(dbg_tail), M, N, K, _stream())
     _lib.check(rc, f"split_gemm_mma(M={M}, N={N}, K={K}, R={R})")
     return out

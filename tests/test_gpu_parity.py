@@ -68,7 +68,7 @@ PROLOGUE_CASES = [
     (O.HAD_WHT, 4096, 3, 4095, "outlier", 100.0),
     (O.HAD_WHT, 4096, 16, 205, "outlier", 98.5),
     (O.HAD_WHT, 8192, 6, 410, "outlier", 100.0),
-    (O.HAD_KRON12, 3072, 6, 154, "outlier", 100.0),
+    (O.HAD_KRON12, 6144, 6, 308, "outlier", 100.0),
     (O.HAD_KRON12, 12288, 20, 615, "outlier", 100.0),
     (O.HAD_BLOCK128, 2048, 6, 103, "outlier", 100.0),
     (O.HAD_BLOCK128, 14336, 12, 717, "outlier", 100.0),
@@ -242,6 +242,24 @@ def _output_bounds(y_bits, y32, slack=0.0):
     assert err.sum() / np.abs(y32).sum() <= 1e-2
 
 
+def tail_records(idx, val_bits, K, cap=16):
+    """The regrouped tail lists the fused GEMM reads: run boundaries, per-slice records and counts."""
+    M, R = idx.shape
+    KB, TM = K // 128, (M + 127) // 128
+    bounds = np.arange(KB + 1, dtype=np.int64) * 128
+    ptr = np.stack([np.searchsorted(idx[m].astype(np.int64), bounds, side="left") for m in range(M)]).astype(np.uint16) \
+        if M else np.zeros((0, KB + 1), np.uint16)
+    rec = np.zeros((TM, KB, cap, 128), np.uint32)
+    cnt = np.zeros((TM, KB, 128), np.uint16)
+    for m in range(M):
+        for kb in range(KB):
+            a, b = int(ptr[m, kb]), int(ptr[m, kb + 1])
+            cnt[m >> 7, kb, m & 127] = b - a
+            for j in range(min(b - a, cap)):
+                rec[m >> 7, kb, j, m & 127] = (int(idx[m, a + j]) & 127) | (int(val_bits[m, a + j]) << 16)
+    return ptr, rec, cnt
+
+
 def permute_q8(codes):
     """INT8 operand order of the fused GEMM: even elements of each 8-group, then the odd ones."""
     M, K = codes.shape
@@ -258,15 +276,24 @@ def test_prologue_int8_operand(kind, K, M, R):
     assert out.a_pack is None
     assert np.array_equal(out.a_q8.cpu().numpy(), permute_q8(ref.codes))
     assert np.array_equal(out.body_scale.cpu().numpy(), ref.body_scale)
+    if R:
+        ptr, rec, cnt = tail_records(ref.idx, ref.tail_val, K)
+        assert np.array_equal(host_bits(out.tail_ptr), ptr), "run boundaries"
+        assert np.array_equal(host_bits(out.tail_cnt), cnt), "entries per slice"
+        got = out.tail_rec.cpu().numpy().view(np.uint32)
+        valid = np.arange(16).reshape(1, 1, 16, 1) < np.minimum(cnt, 16)[:, :, None, :]
+        assert np.array_equal(got[valid], rec[valid]), "slice records"
     both = ops.split_prologue(dev_bf16(xb), kind, R, want_q8=True)
     assert np.array_equal(both.a_pack.cpu().numpy(), ref.a_pack)
     assert np.array_equal(both.a_q8.cpu().numpy(), permute_q8(ref.codes))
 
 
-@pytest.mark.parametrize("M,N,K,R,bias", [(100, 264, 512, 26, True), (256, 512, 1024, 0, False),
-                                          (300, 1032, 4096, 205, False), (129, 136, 12288, 615, True),
-                                          (2048, 512, 256, 13, False), (1, 8, 128, 3, False)])
-def test_split_gemm_mma(M, N, K, R, bias):
+@pytest.mark.parametrize("M,N,K,R,bias,cluster", [(100, 264, 512, 26, True, False), (256, 512, 1024, 0, False, False),
+                                                  (300, 1032, 4096, 205, False, False),
+                                                  (129, 136, 12288, 615, True, False),
+                                                  (2048, 512, 256, 13, False, False), (1, 8, 128, 3, False, False),
+                                                  (140, 264, 1024, 205, False, True)])
+def test_split_gemm_mma(M, N, K, R, bias, cluster):
     """Fused kernel: int32 accumulators bit-exact, tensor-core tail within fp32 accumulation error of the
     fixed-order chain, bf16 output within the stated bounds."""
     rng = np.random.default_rng(M + N + K + R)
@@ -282,6 +309,8 @@ def test_split_gemm_mma(M, N, K, R, bias):
     tv = np.zeros((M, max(ld, 8)), np.uint16)
     if R:
         idx = np.sort(np.argsort(rng.random((M, K)), axis=1)[:, :R], axis=1).astype(np.int32)
+        if cluster:  # runs far longer than a slice record: entries packed into the first slices
+            idx = np.tile(np.arange(R, dtype=np.int32) + 3, (M, 1))
         val = O.f32_to_bf16_bits(rng.standard_normal((M, R), dtype=np.float32) * 3)
         for r_ in range(M):  # tail positions carry code 0 in the dense operand, as the prologue guarantees
             qa[r_, idx[r_]] = 0
@@ -294,11 +323,17 @@ def test_split_gemm_mma(M, N, K, R, bias):
     if bias:
         y = (y + b.reshape(1, -1)).astype(np.float32)
     g = lambda a: torch.from_numpy(a).cuda()
+    pro = None
+    if R:
+        ptr, rec, cnt = tail_records(idx, val, K)
+        pro = ops.PrologueOut(a_pack=None, body_scale=g(sx), top_scale=g(sx), tail_idx=g(ti.view(np.int16)),
+                              tail_val=dev_bf16(tv), R=R, tail_ptr=g(ptr.view(np.int16)), tail_rec=g(rec.view(np.int32)),
+                              tail_cnt=g(cnt.view(np.int16)))
     out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     dacc = torch.empty((M, N), dtype=torch.int32, device="cuda")
     dtail = torch.empty((M, N), dtype=torch.float32, device="cuda")
-    ops.split_gemm_mma(g(permute_q8(qa)), g(sx), g(O.pack_s4(qw)), g(sw), out, w_rot=dev_bf16(w_rot),
-                       tail_idx=g(ti.view(np.int16)), tail_val=dev_bf16(tv), R=R, bias=None if b is None else g(b),
+    ops.split_gemm_mma(g(permute_q8(qa)), g(sx), g(O.pack_s4(qw)), g(sw), out, w_rot=dev_bf16(w_rot), pro=pro, R=R,
+                       bias=None if b is None else g(b),
                        dbg_acc=dacc, dbg_tail=dtail)
     assert np.array_equal(dacc.cpu().numpy(), acc), "int32 accumulators"
     slack = 0.0
