@@ -72,8 +72,10 @@ const char* tq_last_cuda_error(void);
  *   tail_ptr     [M,ptr_ld] u16, ptr_ld >= K/128 + 1: tail_ptr[m][j] = number of tail entries of row m
  *                with index < 128 j (run boundaries for tq_split_gemm_mma; K % 128 == 0; may be NULL)
  *   tail_rec     [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
- *                tile and 128-wide K slice as (index & 127) | bf16 bits << 16, entry j of the 128 rows
- *                contiguous -- what tq_split_gemm_mma reads, one coalesced load per j (may be NULL)
+ *                tile and 128-wide K slice, entry j of the 128 rows contiguous -- what tq_split_gemm_mma
+ *                reads, one coalesced load per j.  Entry = bf16 bits << 16 | (index & 64) | p, where
+ *                p = ((((index & 63) >> 3) ^ (m & 7)) << 3) | (index & 7) is half the byte offset of the
+ *                value in its 128-byte row of the 128-byte-swizzled operand tile (may be NULL)
  *   tail_cnt     [ceil(M/128)][K/128][128] u16 entries per (row, slice) (with tail_rec)
  *   idx32        [M,R] i32 the same indices                          (T4; may be NULL)
  *   top_q        [M,R] i8  clamp(rint(x / top_scale), -8, 7)         (T4; may be NULL)

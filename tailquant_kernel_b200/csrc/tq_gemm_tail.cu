@@ -11,12 +11,12 @@
 // One persistent CTA per SM.  For every 128-wide slice of K a tile consumes three operand slots:
 //   slot kind        A operand [128 rows]                         B operand [BN rows]
 //   int8  (128 k)    INT8 codes of the activations, TMA           INT4 weights: TMA to staging, widened to
-//                    (128-byte swizzle) straight into the slot    INT8 (x16) by the builder warps
+//                    (128-byte swizzle) straight into the slot    INT8 (x16) by warps 2..5
 //   bf16  (64 k) x2  tail values scattered by the builder warps   rotated bf16 weight rows [N,K], TMA
 //                    from the rows' (index, value) lists into a    (128-byte swizzle) straight into the slot
 //                    zero-filled tile
-// Warp roles: 0 = TMA producer, 1 = MMA issuer (+ tensor-memory allocation), 2..5 = epilogue,
-// 6..13 = builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory (no multicast).
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (+ tensor-memory allocation), 2..5 = weight wideners during
+// the main loop and epilogue at the end of the tile, 6..13 = tail-tile builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory (no multicast).
 // Every mbarrier wait is bounded (see mbar_wait).
 //
 // The activation codes arrive as INT8 with the two nibble planes of each 8-element group de-interleaved
@@ -47,7 +47,7 @@ struct SplitGemmParams {
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
-  const uint32_t* rec;   // [tiles_m][K/128][TQ_TAIL_REC_CAP][128]: (index & 127) | bf16 << 16
+  const uint32_t* rec;   // [tiles_m][K/128][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
   const uint16_t* cnt;   // [tiles_m][K/128][128]: entries of the row in the slice
   const float* sx;
   const float* sw;
@@ -101,10 +101,10 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     for (int s = 0; s < S::SP; ++s) {
       mbar_init(full_p(s), 1);
-      mbar_init(empty_p(s), G_BUILD_WARPS / 2);
+      mbar_init(empty_p(s), 4);
     }
     for (int s = 0; s < S::SU; ++s) {
-      mbar_init(full_u(s), G_BUILD_WARPS / 2 + 1);  // four builder warps + the producer's expect_tx arrival
+      mbar_init(full_u(s), 4 + 1);  // four warps (wideners, or the tail builders of one half) + the producer's expect_tx
       mbar_init(empty_u(s), 1);
     }
     mbar_init(acc_full, 1);
@@ -206,12 +206,55 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
       }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------------ wideners + epilogue
+    // These four warps widen the INT4 weight tiles of a tile's K slices, then drain its accumulators.
+    // (The tensor memory holds one accumulator set, so the next tile's MMAs wait for the epilogue anyway.)
     const int quad = warp & 3;
+    const int etid = threadIdx.x - 2 * 32;  // 0..127
     uint32_t pha = 0;
     bool ok = true;
+    int wq = 0, kbg = 0;
+    // INT4 -> INT8 (x16) of one weight tile: staging buffer (kbg mod SP) -> B region of slot use q
+    auto widen = [&](int q, int kbg_) -> bool {
+      const int s = slot_of(q), sp = kbg_ % S::SP;
+      const uint32_t php = (uint32_t)((kbg_ / S::SP) & 1);
+      if (!mbar_wait(full_p(sp), php, abort_flag, 0x80000u)) return false;
+      if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u)) return false;
+      tc_fence_after();
+      const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
+      unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
+#pragma unroll
+      for (int task = etid; task < BN * 4; task += 128) {
+        const int row = task >> 2, piece = task & 3;
+        const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
+        unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
+        uint4 lo, hi;
+        lo.x = (w.x << 4) & 0xf0f0f0f0u;
+        lo.y = w.x & 0xf0f0f0f0u;
+        lo.z = (w.y << 4) & 0xf0f0f0f0u;
+        lo.w = w.y & 0xf0f0f0f0u;
+        hi.x = (w.z << 4) & 0xf0f0f0f0u;
+        hi.y = w.z & 0xf0f0f0f0u;
+        hi.z = (w.w << 4) & 0xf0f0f0f0u;
+        hi.w = w.w & 0xf0f0f0f0u;
+        *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(full_u(s));
+        mbar_arrive(empty_p(sp));
+      }
+      return true;
+    };
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       const int mt = t % p.tiles_m, nt = t / p.tiles_m;
+      for (int kb = 0; kb < p.kb_total && ok; ++kb, ++kbg) {
+        ok = widen(wq, kbg);
+        wq += has_tail ? 3 : 1;
+      }
+      if (!ok) break;
       if (!(ok = mbar_wait(acc_full, pha, abort_flag, 0x40000u))) break;
       tc_fence_after();
       const int row = mt * G_BM + quad * 32 + lane;
@@ -276,69 +319,19 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
       pha ^= 1u;
     }
   } else {
-    // ------------------------------------------------------------------ builders
-    // Two groups of four warps.  With a tail, group 0 widens the INT4 weight tiles and group 1 builds the
-    // bf16 tail tiles, so neither waits for the other's slots; without one, the groups take alternate
-    // K slices of the widening.
-    const int btid = threadIdx.x - 6 * 32;
-    const int grp = btid >> 7, gtid = btid & 127;
-    bool ok = true;
-
-    // INT4 -> INT8 (x16) of one weight tile: staging buffer (kbg mod SP) -> B region of slot use q
-    auto widen = [&](int q, int kbg) -> bool {
-      const int s = slot_of(q), sp = kbg % S::SP;
-      const uint32_t php = (uint32_t)((kbg / S::SP) & 1);
-      if (!mbar_wait(full_p(sp), php, abort_flag, 0x80000u)) return false;
-      if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u)) return false;
-      tc_fence_after();
-      const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
-      unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
-#pragma unroll
-      for (int task = gtid; task < BN * 4; task += 128) {
-        const int row = task >> 2, piece = task & 3;
-        const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
-        unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
-        uint4 lo, hi;
-        lo.x = (w.x << 4) & 0xf0f0f0f0u;
-        lo.y = w.x & 0xf0f0f0f0u;
-        lo.z = (w.y << 4) & 0xf0f0f0f0u;
-        lo.w = w.y & 0xf0f0f0f0u;
-        hi.x = (w.z << 4) & 0xf0f0f0f0u;
-        hi.y = w.z & 0xf0f0f0f0u;
-        hi.z = (w.w << 4) & 0xf0f0f0f0u;
-        hi.w = w.w & 0xf0f0f0f0u;
-        *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(full_u(s));
-        mbar_arrive(empty_p(sp));
-      }
-      return true;
-    };
-
-    if (!has_tail || grp == 0) {
-      int q = 0, kbg = 0;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        for (int kb = 0; kb < p.kb_total && ok; ++kb, ++kbg) {
-          if (has_tail) {
-            ok = widen(q, kbg);
-            q += 3;
-          } else {
-            if ((kbg & 1) == grp) ok = widen(q, kbg);
-            q += 1;
-          }
-        }
-      }
-    } else {
-      // bf16 tail tiles: one thread per row.  The row's entries of a 128-wide K slice come as one record
-      // column ([slice][j][row], so a warp reads 128 contiguous bytes per j), fetched two slices ahead.
+    // ------------------------------------------------------------------ tail builders
+    // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
+    // bf16 tail tile of that half.  The row's entries of a slice come as one record column
+    // ([slice][j][row]: a warp reads 128 contiguous bytes per j), fetched two slices ahead; the record
+    // already holds the swizzled position of the value inside the 128-byte tile row.
+    if (has_tail) {
       constexpr int C = TQ_TAIL_REC_CAP;
-      const int brow = gtid;
+      const int btid = threadIdx.x - 6 * 32;
+      const int brow = btid & 127, half = btid >> 7;
       const uint32_t roff = (uint32_t)((brow >> 3) * 1024 + (brow & 7) * 128);
-      int q = 1;
+      const uint32_t halfbit = (uint32_t)half << 6;
+      bool ok = true;
+      int q = 1 + half;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         const int mt = t % p.tiles_m;
         const int grow = mt * G_BM + brow;
@@ -346,8 +339,6 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
         const uint16_t* cntb = p.cnt + (size_t)mt * p.kb_total * 128 + brow;
         auto fetch = [&](uint32_t(&r)[C], int& n, int kb) {
           if (kb < p.kb_total) {
-            // volatile asm keeps these loads where they are written: ahead of the barrier waits of the
-            // slices in between, so their latency is never on the path "slot free" -> "slot full"
             uint32_t n16;
             asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 128));
             n = (int)n16;
@@ -357,46 +348,33 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
           } else {
             n = 0;
           }
-          // the fetch after this one is pulled towards the SM now, so that when its loads are issued they
-          // return quickly: a proxy fence waits for the thread's outstanding loads, and those fences sit
-          // between "slot free" and "slot full"
-          if (kb + 2 < p.kb_total) {
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(cntb + (size_t)(kb + 2) * 128));
-#pragma unroll
-            for (int j = 0; j < C; ++j)
-              asm volatile("prefetch.global.L1 [%0];" ::"l"(recb + ((size_t)(kb + 2) * C + j) * 128));
-          }
         };
         auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {
+          const int s = slot_of(q);
+          if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u)) return false;
+          tc_fence_after();
+          unsigned char* arow = sm + s * S::SLOT + roff;
+          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int s = slot_of(q + h);
-            if (!mbar_wait(empty_u(s), par_of(q + h) ^ 1u, abort_flag, 0x200000u)) return false;
-            tc_fence_after();
-            unsigned char* arow = sm + s * S::SLOT + roff;
-            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
-#pragma unroll
-            for (int j = 0; j < C; ++j) {
-              const int c = (int)(r[j] & 127u) - 64 * h;  // position inside this 64-wide half
-              if (j < n && c >= 0 && c < 64)
-                *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) = (uint16_t)(r[j] >> 16);
-            }
-            if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list
-              const size_t lrow = (size_t)grow;
-              const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
-              for (int j = C; j < n; ++j) {
-                const int c = (int)__ldg(p.idx + lrow * p.ld + e0 + j) - kb * G_BK - 64 * h;
-                if (c >= 0 && c < 64)
-                  *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
-                      __ldg(p.val + lrow * p.ld + e0 + j);
-              }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_u(s));
+          for (int j = 0; j < C; ++j) {
+            if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
+              *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
           }
+          if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list
+            const size_t lrow = (size_t)grow;
+            const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+            for (int j = C; j < n; ++j) {
+              const int c = (int)__ldg(p.idx + lrow * p.ld + e0 + j) - kb * G_BK - 64 * half;
+              if (c >= 0 && c < 64)
+                *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                    __ldg(p.val + lrow * p.ld + e0 + j);
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full_u(s));
           q += 3;
           return true;
         };

@@ -40,7 +40,7 @@ struct PrologueParams {
   uint16_t* tail_idx16;
   uint16_t* tail_val;
   uint16_t* tail_ptr;  // [M, ptr_ld]: entries with index < 128 * j, j = 0 .. K/128
-  uint32_t* tail_rec;  // [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128]: (index & 127) | bf16 << 16
+  uint32_t* tail_rec;  // [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16
   uint16_t* tail_cnt;  // [ceil(M/128)][K/128][128]: entries per 128-wide slice
   int32_t* idx32;
   int8_t* top_q;
@@ -445,8 +445,10 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
               const uint32_t ps = prefix[(i >> 7) << 3];
               const int j = pos - ((int)(ps & 0xffffu) + min((int)(ps >> 16), need));
               if (j < TQ_TAIL_REC_CAP)
+                // bit 6: which 64-wide half; bits 0..5: half the byte offset of the value inside its
+                // 128-byte row of the swizzled operand tile (16-byte chunk index XOR row & 7, then the element)
                 p.tail_rec[(((size_t)(m >> 7) * (K / 128) + (i >> 7)) * TQ_TAIL_REC_CAP + j) * 128 + (m & 127)] =
-                    (uint32_t)(i & 127) | (vb << 16);
+                    (uint32_t)(i & 64) | (uint32_t)(((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)) | (vb << 16);
             }
             if (p.top_q) st_q[pos] = (int8_t)quant_s4(xv, tscale, trinv);
           }

@@ -256,7 +256,9 @@ def tail_records(idx, val_bits, K, cap=16):
             a, b = int(ptr[m, kb]), int(ptr[m, kb + 1])
             cnt[m >> 7, kb, m & 127] = b - a
             for j in range(min(b - a, cap)):
-                rec[m >> 7, kb, j, m & 127] = (int(idx[m, a + j]) & 127) | (int(val_bits[m, a + j]) << 16)
+                i = int(idx[m, a + j])
+                pos = (i & 64) | ((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)
+                rec[m >> 7, kb, j, m & 127] = pos | (int(val_bits[m, a + j]) << 16)
     return ptr, rec, cnt
 
 
