@@ -196,6 +196,21 @@ int tq_sparse_top_write(void* out, int out_dtype, const int8_t* top_q, const voi
                         int M, int N, int K, int R, void* stream);
 int tq_idx_i32_to_u16(const int32_t* idx, uint16_t* out, long long n, void* stream);
 
+/* Split-K linear for callers that cannot allocate device memory: the same computation as
+ * tq_int4_matmul(split_k) followed by tq_dequant_finish,
+ *   out[m,n] = bf16((float(sum_k qa qw) * body_scale[m]) * w_scale[n] + tail[m,n] + bias[n]),
+ * but the int32 accumulators between the two passes live in a fixed 4 MiB array inside the library instead of
+ * a caller-supplied buffer (M * N <= TQ_NOALLOC_MAX_ELEMS, else TQ_ERR_TOO_LARGE).  `tail` and `bias` may be
+ * NULL.  This entry point has no counterpart in the reference: it exists for hosts whose device memory is
+ * entirely owned by their own pool, or that must not call cudaMalloc/cudaFree in their decode loop.
+ * The array is shared by all calls on a device (the used part is zeroed at the start of each call), so calls
+ * whose GPU work overlaps race; its device address is looked up on the first call on each device, which
+ * should therefore be made once at start-up, before any stream capture begins. */
+#define TQ_NOALLOC_MAX_ELEMS (1 << 20)
+int tq_int4_linear_splitk_noalloc(const uint8_t* a_pack, const float* body_scale, const uint8_t* b_col,
+                                  const float* w_scale, const float* tail, const float* bias, void* out_bf16,
+                                  int M, int N, int K, int split_k, void* stream);
+
 /* Status word of the last GEMM launches on the current device: 0, or a code naming the
  * pipeline wait that ran out of its iteration budget (the kernel then drains and returns
  * instead of spinning).  Synchronises the device. */

@@ -25,6 +25,8 @@
 // and the dequant `scale_i32_to_fp16` that follows it (same file :262,283).
 #include <cuda.h>
 
+#include <mutex>
+
 #include "tq_common.cuh"
 #include "tq_ptx.cuh"
 
@@ -417,4 +419,106 @@ extern "C" int tq_gemm_status(unsigned int* status) {
     return TQ_ERR_CUDA;
   }
   return *status ? TQ_ERR_DEVICE_STATUS : TQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Split-K linear without any allocation by anybody: the int32 accumulators that the split-K GEMM needs
+// between its atomic adds and the finishing pass live in a fixed array inside the library image instead of
+// in a buffer handed in by the caller.
+//
+// Who needs this: a host that may not, or cannot, obtain device memory at the time it runs a small-M linear.
+// Typical cases are a serving process that gave the whole device to its own memory pool at start-up (a later
+// cudaMalloc then fails or eats into the pool's headroom), a decode loop in a plain C/C++ host that has no
+// caching allocator and must not call cudaMalloc/cudaFree per token because both synchronise the device, and
+// plug-in style code whose execute callback is forbidden to allocate.  Such a caller still owns its inputs
+// and its output; only the intermediate accumulators come from here.
+//
+// Limits and rules:
+//  * M * N <= TQ_NOALLOC_MAX_ELEMS (1 Mi accumulators = 4 MiB).  Every GPU that loads the library carries the
+//    array in its module image until the process exits, which is why it is kept this small.
+//  * The array is shared by all calls on a device and keeps whatever the last call left: this entry point
+//    zeroes the M * N accumulators it is about to use at the start of every call.  Two calls whose GPU work
+//    overlaps (different streams, or different host threads on different streams) race on it; serialise them.
+//  * The device address of the array is looked up with cudaGetSymbolAddress on the first call on each device
+//    (with that device current) and cached.  Make that first call once during start-up, before any stream
+//    capture is begun on the device.
+//  * No cudaMalloc, cudaFree or allocating library routine is called here.
+namespace tq {
+namespace {
+
+static __device__ __align__(256) int32_t g_noalloc_acc[TQ_NOALLOC_MAX_ELEMS];
+
+// In host code the array's name only stands in for the symbol; the kernels need its device address.
+int32_t* noalloc_acc_ptr(int* rc) {
+  static std::mutex mu;
+  static int32_t* ptrs[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && (dev < 0 || dev >= 64)) e = cudaErrorInvalidDevice;
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    *rc = TQ_ERR_CUDA;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_acc);
+    if (e != cudaSuccess || !ptr) {
+      set_last_cuda_error(e == cudaSuccess ? cudaErrorInvalidSymbol : e);
+      *rc = TQ_ERR_CUDA;
+      return nullptr;
+    }
+    ptrs[dev] = reinterpret_cast<int32_t*>(ptr);
+  }
+  *rc = TQ_OK;
+  return ptrs[dev];
+}
+
+__global__ void noalloc_finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sx,
+                                      const float* __restrict__ sw, const float* __restrict__ tail,
+                                      const float* __restrict__ bias, uint16_t* __restrict__ out, int M, int N) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  float d = __fmul_rn(__fmul_rn((float)acc[i], sx[m]), sw[n]);
+  if (tail) d = __fadd_rn(d, tail[i]);
+  if (bias) d = __fadd_rn(d, bias[n]);
+  out[i] = (uint16_t)f32_to_bf16_bits(d);
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" int tq_int4_linear_splitk_noalloc(const uint8_t* a_pack, const float* body_scale, const uint8_t* b_col,
+                                             const float* w_scale, const float* tail, const float* bias,
+                                             void* out_bf16, int M, int N, int K, int split_k, void* stream) {
+  using namespace tq;
+  if (!a_pack || !body_scale || !b_col || !w_scale || !out_bf16 || M < 0 || N <= 0 || K <= 0) return TQ_ERR_BAD_ARG;
+  if ((unsigned long long)M * (unsigned long long)N > (unsigned long long)TQ_NOALLOC_MAX_ELEMS) return TQ_ERR_TOO_LARGE;
+  if (K % BK != 0 || N % 8 != 0) return TQ_ERR_UNSUPPORTED;
+  if (!aligned16(a_pack) || !aligned16(b_col)) return TQ_ERR_MISALIGNED;
+  if (M == 0) return TQ_OK;
+  int rc = TQ_OK;
+  int32_t* acc = noalloc_acc_ptr(&rc);
+  if (!acc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t total = (size_t)M * N;
+  cudaError_t e = cudaMemsetAsync(acc, 0, total * sizeof(int32_t), st);  // the atomic adds need zeros
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return TQ_ERR_CUDA;
+  }
+  GemmParams p = {};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.split_k = split_k < 1 ? 1 : split_k;
+  p.mode = MODE_I32_ATOMIC;
+  p.C = acc;
+  rc = run_gemm(a_pack, b_col, p, st);
+  if (rc != TQ_OK) return rc;
+  noalloc_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+      acc, body_scale, w_scale, tail, bias, reinterpret_cast<uint16_t*>(out_bf16), M, N);
+  return check_launch();
 }

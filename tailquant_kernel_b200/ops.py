@@ -318,6 +318,26 @@ def dequant_finish(C, body_scale, w_scale, out, tail=None, bias=None):
     return out
 
 
+NOALLOC_MAX_ELEMS = 1 << 20  # TQ_NOALLOC_MAX_ELEMS of include/tailquant.h
+
+
+def linear_splitk_noalloc(A_pack, body_scale, B_pack, w_scale, out, split_k: int, tail=None, bias=None):
+    """Split-K linear whose int32 accumulators live in a fixed array inside libtailquant.so, for hosts that
+    cannot allocate device memory when they run it (M * N <= NOALLOC_MAX_ELEMS).  Same result as
+    matmul_splitk + dequant_finish.  Calls on one device share the array: do not let two of them overlap on
+    the GPU, and make the first call on a device during start-up."""
+    M, N, K = _gemm_dims(A_pack, B_pack, None, None, None)
+    _check_cuda(body_scale, "body_scale", torch.float32)
+    _check_cuda(w_scale, "w_scale", torch.float32)
+    _check_cuda(out, "out", torch.bfloat16)
+    _check(out.numel() >= M * N, "out too small")
+    rc = _lib.load().tq_int4_linear_splitk_noalloc(_ptr(A_pack), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale),
+                                                   _ptr(tail), _ptr(bias), _ptr(out), M, N, K, int(split_k),
+                                                   _stream())
+    _lib.check(rc, f"linear_splitk_noalloc(M={M}, N={N}, K={K}, split_k={split_k})")
+    return out
+
+
 def tail_gather(tail_idx, tail_val, w_t, tail_out, R: int):
     """tail_out[m,n] = sum_r tail_val[m,r] * w_t[tail_idx[m,r], n] (fp32 fma chain, ascending r)."""
     _check_cuda(tail_idx, "tail_idx", torch.int16)
