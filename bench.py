@@ -39,6 +39,9 @@ RATIO = 0.05
 CPU_SAMPLE_ROWS = 64
 METRIC = "split W4A4+tail linear TOPS, Qwen3-8B layer shapes, prefill M=2048/GPU, ratio 0.05"
 NOMINAL_INT8_TOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum of the four split_gemm_kernel launches of one step, from the ncu
+# capture summarised in profiles/split_gemm_kernel_qwen3_layer_m2048.md (bytes)
+GEMM_DRAM_BYTES_PER_STEP = int((265.1 + 82.1 + 208.9 + 12.9 + 76.3 + 9.1 + 54.8 + 1.8) * 1e6)
 
 
 def layer_ops(m: int) -> float:
@@ -146,7 +149,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.01)
+            time.sleep(0.002)
 
     def start(self):
         if self.nv is not None:
@@ -339,7 +342,7 @@ def run_ours(args) -> None:
         "clocks": clocks,
         "roofline": {"kernel": kname, "bound": "tensor",
                      "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
-                     "traffic": None,
+                     "traffic": GEMM_DRAM_BYTES_PER_STEP if mma else None,
                      "peak_note": f"2 x sustained bf16 cuBLAS figure ({peaks['source']}); nominal dense INT8 {NOMINAL_INT8_TOPS}; "
                                   "achieved counts the algorithmic 2*M*N*K of the INT4 product only",
                      "frac_of_nominal_int8": gemm_tops / NOMINAL_INT8_TOPS,
@@ -377,16 +380,94 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------- other baseline configs
+def run_extra(args) -> None:
+    """Secondary workloads of the baseline (one JSON line per case, device time by CUDA events):
+    decode      : Qwen3-8B layer shapes at M in {1, 8, 32, 64}, split-K path, int4-weight GB/s against HBM peak
+    llama_sweep : Llama-3-8B layer shapes at M = 4096, ratios 0 / 0.01 / 0.05 / 0.10 (K = 14336 uses block-128)
+    single      : baseline config 1 (M = 512, K = N = 4096, ratio 0.05), both tail engines"""
+    import torch
+    from tailquant_kernel_b200 import SplitLinear
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+
+    def ms_of(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def data(M, K, N, seed):
+        g = torch.Generator(device="cpu")
+        g.manual_seed(seed)
+        W = (torch.randn((N, K), generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        x = torch.randn((M, K), generator=g)
+        x[:, torch.randperm(K, generator=g)[: max(16, K // 100)]] *= 50.0
+        return x.to(torch.bfloat16).to(dev), W
+
+    if args.workload == "decode":
+        for name, K, N in LAYER:
+            _, W = data(1, K, N, 7)
+            lin = SplitLinear(W, ratio=RATIO, tail_engine="gather")
+            for M in (1, 8, 32, 64):
+                x, _ = data(M, K, N, 11 + M)
+                ws = lin.prologue(x)
+                t_all = ms_of(lambda: lin.forward(x))
+                t_gemm = ms_of(lambda: __import__("tailquant_kernel_b200").ops.matmul_splitk(
+                    ws.pro.a_pack, lin.w.b_col, ws.acc, lin._pick_split_k(M)))
+                wbytes = K * N / 2
+                print(json.dumps({"workload": "decode", "linear": name, "M": M, "K": K, "N": N, "R": lin.R,
+                                  "split_k": lin._pick_split_k(M), "linear_ms": t_all, "splitk_gemm_ms": t_gemm,
+                                  "int4_weight_gbs": wbytes / (t_gemm * 1e-3) / 1e9,
+                                  "frac_of_hbm_peak": wbytes / (t_gemm * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                  "tail_row_bytes": 2.0 * M * lin.R * N}), flush=True)
+    elif args.workload == "llama_sweep":
+        shapes = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
+        M = 4096
+        for name, K, N in shapes:
+            x, W = data(M, K, N, 3)
+            bf = ms_of(lambda: torch.nn.functional.linear(x, W))
+            for ratio in (0.0, 0.01, 0.05, 0.10):
+                lin = SplitLinear(W, ratio=ratio)
+                t = ms_of(lambda: lin.forward(x))
+                print(json.dumps({"workload": "llama_sweep", "linear": name, "M": M, "K": K, "N": N, "ratio": ratio,
+                                  "R": lin.R, "split_ms": t, "bf16_ms": bf, "split_over_bf16": t / bf,
+                                  "tops": 2.0 * M * N * K / (t * 1e-3) / 1e12}), flush=True)
+                del lin
+    else:
+        M, K, N = 512, 4096, 4096
+        x, W = data(M, K, N, 0)
+        bf = ms_of(lambda: torch.nn.functional.linear(x, W))
+        for eng in ("mma", "gather"):
+            lin = SplitLinear(W, ratio=RATIO, tail_engine=eng)
+            t = ms_of(lambda: lin.forward(x))
+            print(json.dumps({"workload": "single", "tail_engine": eng, "M": M, "K": K, "N": N, "R": lin.R,
+                              "split_ms": t, "bf16_ms": bf, "tops": 2.0 * M * N * K / (t * 1e-3) / 1e12}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tail-engine", default="mma", choices=["mma", "gather"],
                     help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
+    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single"],
+                    help="layer = the benchmark proper (baseline configs[1]); the others print secondary figures")
     args = ap.parse_args()
+    if args.workload != "layer":
+        run_extra(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

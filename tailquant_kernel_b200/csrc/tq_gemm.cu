@@ -4,7 +4,7 @@
 //
 // One persistent CTA per SM, 14 warps with fixed roles:
 //   warp 0        TMA producer: packed A [128 x 64 B] and B [BN x 64 B] tiles of one 128-wide
-//                 k-block into a ring of staging buffers (no multicast, plain 2-D tiled loads)
+//                 k-block into a ring of staging buffers (plain 2-D tiled loads, one CTA each)
 //   warps 6..13   unpackers: read 16 packed bytes, widen the 32 nibbles to INT8 (value x 16,
 //                 sign kept in the top nibble, so no sign extension is needed) and store them
 //                 into the canonical K-major 128-byte-swizzled UMMA operand layout

@@ -16,7 +16,7 @@
 //                    from the rows' (index, value) lists into a    (128-byte swizzle) straight into the slot
 //                    zero-filled tile
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (+ tensor-memory allocation), 2..5 = weight wideners during
-// the main loop and epilogue at the end of the tile, 6..13 = tail-tile builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory (no multicast).
+// the main loop and epilogue at the end of the tile, 6..13 = tail-tile builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory, issued per CTA.
 // Every mbarrier wait is bounded (see mbar_wait).
 //
 // The activation codes arrive as INT8 with the two nibble planes of each 8-element group de-interleaved
