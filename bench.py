@@ -405,6 +405,22 @@ def run_extra(args) -> None:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
+    def graph_ms_of(fn, reps=50):
+        """Device time of fn replayed from a CUDA graph (host launch cost excluded), as the reference times
+        its layers (tools/bench_hadamard_three_schemes_quarot_dense_sharedqkv_inplace_fusedtopr_v43.py:105-123)."""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        return ms_of(graph.replay, reps)
+
     def data(M, K, N, seed):
         g = torch.Generator(device="cpu")
         g.manual_seed(seed)
@@ -420,12 +436,15 @@ def run_extra(args) -> None:
             for M in (1, 8, 32, 64):
                 x, _ = data(M, K, N, 11 + M)
                 ws = lin.prologue(x)
-                t_all = ms_of(lambda: lin.forward(x))
-                t_gemm = ms_of(lambda: __import__("tailquant_kernel_b200").ops.matmul_splitk(
-                    ws.pro.a_pack, lin.w.b_col, ws.acc, lin._pick_split_k(M)))
+                from tailquant_kernel_b200 import ops as _ops
+                t_all = graph_ms_of(lambda: lin.forward(x))
+                t_gemm = graph_ms_of(lambda: _ops.gemv_splitk(ws.pro.a_pack, lin.w.b_col, ws.acc, 0))
+                t_pro = graph_ms_of(lambda: lin.prologue(x))
+                t_tail = graph_ms_of(lambda: _ops.tail_gather_small(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R))
                 wbytes = K * N / 2
                 print(json.dumps({"workload": "decode", "linear": name, "M": M, "K": K, "N": N, "R": lin.R,
-                                  "split_k": lin._pick_split_k(M), "linear_ms": t_all, "splitk_gemm_ms": t_gemm,
+                                  "linear_ms": t_all, "splitk_gemm_ms": t_gemm,
+                                  "prologue_ms": t_pro, "tail_gather_ms": t_tail, "timing": "CUDA graph replay",
                                   "int4_weight_gbs": wbytes / (t_gemm * 1e-3) / 1e9,
                                   "frac_of_hbm_peak": wbytes / (t_gemm * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                   "tail_row_bytes": 2.0 * M * lin.R * N}), flush=True)

@@ -171,6 +171,18 @@ int tq_dequant_finish(const int32_t* C, const float* body_scale, const float* w_
 int tq_tail_gather(const uint16_t* tail_idx16, const void* tail_val, const void* w_t,
                    float* tail, int M, int N, int K, int R, int tail_ld, void* stream);
 
+/* Small-M (decode) variants, M <= 64.  The reference has no separate small-M path (its decode bench runs
+ * the prefill kernels at M = 16/64/256: tools/bench_qwen3_decode_split_romeo_quarot_v33.py:36,97-108).
+ * tq_int4_gemv_splitk: C [M,N] i32 = exact INT4 x INT4 product, weights streamed once at HBM speed, the
+ *   reduction split over `split_k` CTAs per 64 output channels (split_k < 1 picks it); C is zeroed by the call.
+ *   The activations come either packed (a_pack) or as the prologue's INT8 operand (a_q8): exactly one is given.
+ * tq_tail_gather_small: the tail sums, reading only the M*R weight rows they need; per output eight
+ *   interleaved fp32 fma chains (entry r on chain r mod 8) combined as ((c0+c1)+(c2+c3))+((c4+c5)+(c6+c7)). */
+int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* C, int M,
+                        int N, int K, int split_k, void* stream);
+int tq_tail_gather_small(const uint16_t* tail_idx16, const void* tail_val, const void* w_t, float* tail,
+                         int M, int N, int K, int R, int tail_ld, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Reference-compatible tail mode T4 (INT4 tail codes against the INT4 weight rows).
  *

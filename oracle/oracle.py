@@ -334,14 +334,34 @@ def tail_t16(idx: np.ndarray, tail_val_bits: np.ndarray, w_rot_bits) -> np.ndarr
     return acc
 
 
+def tail_t16_chains(idx: np.ndarray, tail_val_bits: np.ndarray, w_rot_bits, chains: int = 8) -> np.ndarray:
+    """The tail sum in the order of the small-M kernel: entry r goes to chain r mod `chains`, each chain is a
+    left-to-right fp32 fma chain, and the chains are combined pairwise: ((c0+c1)+(c2+c3))+((c4+c5)+(c6+c7))."""
+    M, R = idx.shape
+    wt = w_rot_bits.w_t_f32() if isinstance(w_rot_bits, PreparedWeight) else \
+        np.ascontiguousarray(bf16_bits_to_f32(w_rot_bits).T)
+    N = wt.shape[1]
+    xv = bf16_bits_to_f32(tail_val_bits)
+    parts = [np.zeros((M, N), dtype=np.float32) for _ in range(chains)]
+    for r in range(R):
+        c = r % chains
+        parts[c] = parts[c] + xv[:, r:r + 1] * wt[idx[:, r]]
+    while len(parts) > 1:
+        parts = [(parts[i] + parts[i + 1]).astype(np.float32) for i in range(0, len(parts), 2)]
+    return parts[0]
+
+
 def split_linear_t16(x_bits: np.ndarray, w: PreparedWeight, kind: int, R: int,
-                     bias: Optional[np.ndarray] = None, descending_rank: Optional[int] = None):
-    """Full path, tail mode T16.  Returns (bf16 bits [M,N], fp32 pre-rounding, Prologue, int32 acc)."""
+                     bias: Optional[np.ndarray] = None, descending_rank: Optional[int] = None,
+                     tail_chains: int = 1):
+    """Full path, tail mode T16.  Returns (bf16 bits [M,N], fp32 pre-rounding, Prologue, int32 acc).
+    tail_chains = 1: one fma chain per output (prefill gather kernel); 8: the small-M kernel's order."""
     p = prologue(x_bits, kind, R, descending_rank)
     acc = int_gemm(p.codes, w)
     y = dequant(acc, p.body_scale, w.w_scale)
     if R:
-        y = (y + tail_t16(p.idx, p.tail_val, w)).astype(np.float32)
+        t = tail_t16(p.idx, p.tail_val, w) if tail_chains == 1 else tail_t16_chains(p.idx, p.tail_val, w, tail_chains)
+        y = (y + t).astype(np.float32)
     if bias is not None:
         y = (y + bias.astype(np.float32).reshape(1, -1)).astype(np.float32)
     return f32_to_bf16_bits(y), y, p, acc

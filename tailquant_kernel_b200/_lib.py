@@ -34,6 +34,8 @@ SIGNATURES = {
     "tq_sparse_top_write": [_P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "tq_idx_i32_to_u16": [_P, _P, _LL, _P],
     "tq_int4_linear_splitk_noalloc": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tq_int4_gemv_splitk": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tq_tail_gather_small": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "tq_gemm_status": [_P],
 }
 _CHAR_P_RETURNS = {"tq_error_string", "tq_last_cuda_error"}

@@ -6,3 +6,4 @@
 #include "tq_gemm_tail.cu"
 #include "tq_tail.cu"
 #include "tq_misc.cu"
+#include "tq_decode.cu"

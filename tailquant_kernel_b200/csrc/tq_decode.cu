@@ -1,0 +1,267 @@
+// Small-M (decode) path, M <= 64 token rows: HBM-bound streaming of the INT4 weights.
+//
+//  * gemv_s4_kernel: C[m,n] += sum_k qa[m,k] qw[n,k] over one K range (split-K over blockIdx.y), exact int32.
+//    A CTA owns 64 output channels: its eight warps take eight channels each and stream their packed weight
+//    rows with one 128-bit load per lane and 128-wide K slice; the (few) activation rows of the K range are
+//    staged once in shared memory.  Both operands are widened with the same nibble order (value x 16 in the
+//    top nibble, exact >> 8 afterwards) and multiplied with mma.sync m16n8k32 s8: with at most 64 rows the
+//    tensor-core rate is irrelevant, the weight stream is what takes time.  Partial sums are added with int32
+//    atomics into C, which the entry point zeroes first (integer addition: any order gives the same bits).
+//  * tail_small_kernel: the tail correction for few rows reads only the weight rows it needs (M*R rows of the
+//    [K,N] bf16 matrix) instead of streaming whole strips.  The sum over the R entries is split into eight
+//    interleaved fp32 fma chains (entry r goes to chain r mod 8) that are combined pairwise in a fixed order,
+//    which is what the CPU oracle states for this path.
+//
+// Reference behaviour covered: the reference has no small-M path of its own (its decode bench runs the same
+// kernels at M = 16/64/256: tools/bench_qwen3_decode_split_romeo_quarot_v33.py:36,97-108).
+#include "tq_common.cuh"
+
+namespace tq {
+namespace {
+
+constexpr int DV_THREADS = 256;
+constexpr int DV_CH = 64;     // channels per CTA
+constexpr int DV_KS = 128;    // K slice per step
+
+__device__ __forceinline__ void widen16(const uint4& w, uint32_t (&o)[8]) {
+  o[0] = (w.x << 4) & 0xf0f0f0f0u;
+  o[1] = w.x & 0xf0f0f0f0u;
+  o[2] = (w.y << 4) & 0xf0f0f0f0u;
+  o[3] = w.y & 0xf0f0f0f0u;
+  o[4] = (w.z << 4) & 0xf0f0f0f0u;
+  o[5] = w.z & 0xf0f0f0f0u;
+  o[6] = (w.w << 4) & 0xf0f0f0f0u;
+  o[7] = w.w & 0xf0f0f0f0u;
+}
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MT = number of 16-row tiles of the activations (M <= 16 * MT).  A8: the activations arrive as INT8 codes in
+// the operand order of the prologue's a_q8 output (which is the byte order widen16 produces), so their
+// fragments are plain loads; otherwise they arrive packed and are widened like the weights.
+template <int MT, bool A8>
+__global__ void __launch_bounds__(DV_THREADS)
+gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b_col, int32_t* __restrict__ C, int M,
+               int N, int K, int k_per_split) {
+  extern __shared__ __align__(16) unsigned char sm_a[];  // [16*MT rows][pitch] packed activations of this K range
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const int k0 = blockIdx.y * k_per_split;
+  const int k1 = min(K, k0 + k_per_split);
+  if (k0 >= k1) return;
+  constexpr int AB = A8 ? 1 : 2;           // K elements per activation byte
+  const int kbytes = (k1 - k0) / AB;       // activation bytes per row in this range
+  const int pitch = kbytes + 64;           // consecutive rows start 64 bytes apart modulo 128: no bank conflicts
+
+  for (int i = tid; i < 16 * MT * (kbytes / 16); i += DV_THREADS) {
+    const int row = i / (kbytes / 16), piece = i % (kbytes / 16);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < M) v = *reinterpret_cast<const uint4*>(a_pack + (size_t)row * (K / AB) + k0 / AB + piece * 16);
+    *reinterpret_cast<uint4*>(sm_a + row * pitch + piece * 16) = v;
+  }
+  __syncthreads();
+
+  const int n = blockIdx.x * DV_CH + warp * 8 + g;  // channel whose weights this lane streams
+  const uint8_t* wrow = b_col + (size_t)min(n, N - 1) * (K / 2) + k0 / 2 + j * 16;
+  int acc[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+
+  const int nslices = (k1 - k0) / DV_KS;
+  constexpr int PF = 4;  // weight loads kept in flight per lane
+  uint4 wq[PF];
+#pragma unroll
+  for (int s = 0; s < PF; ++s)
+    wq[s] = (s < nslices && n < N) ? ldg_nc_128(wrow + (size_t)s * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+  for (int s0 = 0; s0 < nslices; s0 += PF) {
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+      const int s = s0 + u;
+      if (s < nslices) {
+        uint32_t b[8];
+        widen16(wq[u], b);
+        const int sn = s + PF;
+        wq[u] = (sn < nslices && n < N) ? ldg_nc_128(wrow + (size_t)sn * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          uint32_t a[8], c[8];
+          if (A8) {
+            const unsigned char* plo = sm_a + (16 * t + g) * pitch + s * DV_KS + j * 32;
+            const unsigned char* phi = sm_a + (16 * t + g + 8) * pitch + s * DV_KS + j * 32;
+            const uint4 l0 = *reinterpret_cast<const uint4*>(plo), l1 = *reinterpret_cast<const uint4*>(plo + 16);
+            const uint4 h0 = *reinterpret_cast<const uint4*>(phi), h1 = *reinterpret_cast<const uint4*>(phi + 16);
+            a[0] = l0.x, a[1] = l0.y, a[2] = l0.z, a[3] = l0.w, a[4] = l1.x, a[5] = l1.y, a[6] = l1.z, a[7] = l1.w;
+            c[0] = h0.x, c[1] = h0.y, c[2] = h0.z, c[3] = h0.w, c[4] = h1.x, c[5] = h1.y, c[6] = h1.z, c[7] = h1.w;
+          } else {
+            const uint4 alo = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g) * pitch + s * (DV_KS / 2) + j * 16);
+            const uint4 ahi = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g + 8) * pitch + s * (DV_KS / 2) + j * 16);
+            widen16(alo, a);
+            widen16(ahi, c);
+          }
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) mma_s8(acc[t], a[2 * qd], c[2 * qd], a[2 * qd + 1], c[2 * qd + 1], b[2 * qd], b[2 * qd + 1]);
+        }
+      }
+    }
+  }
+
+  // accumulator fragment: rows g and g + 8 of the tile, channels 2j and 2j + 1 of the warp's eight
+  const int nc = blockIdx.x * DV_CH + warp * 8 + 2 * j;
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = 16 * t + g + ((i >> 1) << 3), col = nc + (i & 1);
+      if (row < M && col < N) atomicAdd(C + (size_t)row * N + col, acc[t][i] >> (A8 ? 4 : 8));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- tail, few rows
+constexpr int TS_THREADS = 256;   // 8 warps = 8 interleaved chains, 32 lanes x 8 columns = 256 columns per CTA
+
+__global__ void __launch_bounds__(TS_THREADS)
+tail_small_kernel(const uint16_t* __restrict__ idx, const uint16_t* __restrict__ val, const uint16_t* __restrict__ w_t,
+                  float* __restrict__ out, int N, int R, int ld) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  uint16_t* s_idx = reinterpret_cast<uint16_t*>(sm_raw);
+  uint16_t* s_val = s_idx + ((R + 7) & ~7);
+  float* s_part = reinterpret_cast<float*>(s_val + ((R + 7) & ~7));  // [8][256]
+  const int tid = threadIdx.x, chain = tid >> 5, lane = tid & 31;
+  const int m = blockIdx.y;
+  const int n = blockIdx.x * 256 + lane * 8;
+  for (int r = tid; r < R; r += TS_THREADS) {
+    s_idx[r] = idx[(size_t)m * ld + r];
+    s_val[r] = val[(size_t)m * ld + r];
+  }
+  __syncthreads();
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  if (n < N) {
+    constexpr int U = 4;
+    for (int r0 = chain; r0 < R; r0 += 8 * U) {
+      uint4 w[U];
+      float x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int r = r0 + 8 * u;
+        const bool in = r < R;
+        x[u] = in ? bf16_bits_to_f32(s_val[r]) : 0.0f;
+        w[u] = in ? ldg_nc_128(w_t + (size_t)s_idx[r] * N + n) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (r0 + 8 * u < R) {
+          acc[0] = fmaf(x[u], __uint_as_float(w[u].x << 16), acc[0]);
+          acc[1] = fmaf(x[u], __uint_as_float(w[u].x & 0xffff0000u), acc[1]);
+          acc[2] = fmaf(x[u], __uint_as_float(w[u].y << 16), acc[2]);
+          acc[3] = fmaf(x[u], __uint_as_float(w[u].y & 0xffff0000u), acc[3]);
+          acc[4] = fmaf(x[u], __uint_as_float(w[u].z << 16), acc[4]);
+          acc[5] = fmaf(x[u], __uint_as_float(w[u].z & 0xffff0000u), acc[5]);
+          acc[6] = fmaf(x[u], __uint_as_float(w[u].w << 16), acc[6]);
+          acc[7] = fmaf(x[u], __uint_as_float(w[u].w & 0xffff0000u), acc[7]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s_part[chain * 256 + lane * 8 + i] = acc[i];
+  __syncthreads();
+  const int col = blockIdx.x * 256 + tid;
+  if (col < N) {
+    float p[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) p[c] = s_part[c * 256 + tid];
+    const float s = __fadd_rn(__fadd_rn(__fadd_rn(p[0], p[1]), __fadd_rn(p[2], p[3])),
+                              __fadd_rn(__fadd_rn(p[4], p[5]), __fadd_rn(p[6], p[7])));
+    out[(size_t)m * N + col] = s;
+  }
+}
+
+template <int MT, bool A8>
+int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, int N, int K, int kps, int splits,
+                cudaStream_t st) {
+  const size_t smem = (size_t)16 * MT * (kps / (A8 ? 1 : 2) + 64);
+  auto kern = gemv_s4_kernel<MT, A8>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && !(dev < 64 && configured[dev])) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return TQ_ERR_CUDA;
+    }
+    if (dev < 64) configured[dev] = true;
+  }
+  dim3 grid((N + DV_CH - 1) / DV_CH, splits);
+  kern<<<grid, DV_THREADS, smem, st>>>(a_pack, b_col, C, M, N, K, kps);
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* C, int M,
+                                   int N, int K, int split_k, void* stream) {
+  using namespace tq;
+  if ((a_pack == nullptr) == (a_q8 == nullptr) || !b_col || !C || M < 0 || N <= 0 || K <= 0) return TQ_ERR_BAD_ARG;
+  if (M > 64 || K % DV_KS != 0) return TQ_ERR_UNSUPPORTED;
+  const bool a8 = a_q8 != nullptr;
+  const uint8_t* a = a8 ? reinterpret_cast<const uint8_t*>(a_q8) : a_pack;
+  if (!aligned16(a) || !aligned16(b_col)) return TQ_ERR_MISALIGNED;
+  if (M == 0) return TQ_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int slices = K / DV_KS;
+  if (split_k < 1) {  // enough CTAs for a few per SM, at least two K slices each
+    const int ctas_n = (N + DV_CH - 1) / DV_CH;
+    split_k = (4 * 148 + ctas_n - 1) / ctas_n;
+  }
+  if (split_k > slices) split_k = slices;
+  int sps = (slices + split_k - 1) / split_k;                 // slices per split
+  const int max_sps = (180 * 1024 / (16 * ((M + 15) / 16)) - 64) / (a8 ? DV_KS : DV_KS / 2);  // activation rows must fit in shared memory
+  if (sps > max_sps) sps = max_sps;
+  const int splits = (slices + sps - 1) / sps;
+  cudaError_t e = cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), st);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return TQ_ERR_CUDA;
+  }
+  const int kps = sps * DV_KS;
+  const int mt = (M + 15) / 16;
+  if (a8) {
+    if (mt == 1) return launch_gemv<1, true>(a, b_col, C, M, N, K, kps, splits, st);
+    if (mt == 2) return launch_gemv<2, true>(a, b_col, C, M, N, K, kps, splits, st);
+    if (mt == 3) return launch_gemv<3, true>(a, b_col, C, M, N, K, kps, splits, st);
+    return launch_gemv<4, true>(a, b_col, C, M, N, K, kps, splits, st);
+  }
+  if (mt == 1) return launch_gemv<1, false>(a, b_col, C, M, N, K, kps, splits, st);
+  if (mt == 2) return launch_gemv<2, false>(a, b_col, C, M, N, K, kps, splits, st);
+  if (mt == 3) return launch_gemv<3, false>(a, b_col, C, M, N, K, kps, splits, st);
+  return launch_gemv<4, false>(a, b_col, C, M, N, K, kps, splits, st);
+}
+
+extern "C" int tq_tail_gather_small(const uint16_t* tail_idx16, const void* tail_val, const void* w_t, float* tail,
+                                    int M, int N, int K, int R, int tail_ld, void* stream) {
+  using namespace tq;
+  if (!tail_idx16 || !tail_val || !w_t || !tail || M < 0 || N <= 0 || K <= 0 || R <= 0 || R >= K || tail_ld < R)
+    return TQ_ERR_BAD_ARG;
+  if (N % 8 != 0 || R > 8192) return TQ_ERR_UNSUPPORTED;
+  if (!aligned16(w_t)) return TQ_ERR_MISALIGNED;
+  if (M == 0) return TQ_OK;
+  const size_t smem = (size_t)((R + 7) & ~7) * 4 + 8 * 256 * sizeof(float);
+  dim3 grid((N + 255) / 256, M);
+  tail_small_kernel<<<grid, TS_THREADS, smem, (cudaStream_t)stream>>>(
+      tail_idx16, reinterpret_cast<const uint16_t*>(tail_val), reinterpret_cast<const uint16_t*>(w_t), tail, N, R,
+      tail_ld);
+  return check_launch();
+}

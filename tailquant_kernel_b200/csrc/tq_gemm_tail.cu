@@ -362,14 +362,33 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
             if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
               *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
           }
-          if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list
+          if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
             const size_t lrow = (size_t)grow;
             const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
-            for (int j = C; j < n; ++j) {
-              const int c = (int)__ldg(p.idx + lrow * p.ld + e0 + j) - kb * G_BK - 64 * half;
-              if (c >= 0 && c < 64)
-                *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
-                    __ldg(p.val + lrow * p.ld + e0 + j);
+            const int lo = e0 + C, hi = e0 + n;  // list positions [lo, hi)
+            const int kb0 = kb * G_BK + 64 * half;
+            if ((p.ld & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.val)) & 15) == 0) {
+              const uint4* irow = reinterpret_cast<const uint4*>(p.idx + lrow * p.ld);
+              const uint4* vrow = reinterpret_cast<const uint4*>(p.val + lrow * p.ld);
+              for (int g8 = lo >> 3; g8 <= (hi - 1) >> 3; ++g8) {
+                const uint4 gi = __ldg(irow + g8), gv = __ldg(vrow + g8);
+                const uint32_t wi[4] = {gi.x, gi.y, gi.z, gi.w}, wv[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  const int e = g8 * 8 + u;
+                  const int c = (int)((wi[u >> 1] >> ((u & 1) * 16)) & 0xffffu) - kb0;
+                  if (e >= lo && e < hi && c >= 0 && c < 64)
+                    *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                        (uint16_t)(wv[u >> 1] >> ((u & 1) * 16));
+                }
+              }
+            } else {
+              for (int e = lo; e < hi; ++e) {
+                const int c = (int)__ldg(p.idx + lrow * p.ld + e) - kb0;
+                if (c >= 0 && c < 64)
+                  *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                      __ldg(p.val + lrow * p.ld + e);
+              }
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -19,11 +19,12 @@ from . import ops
 
 
 class _Workspace:
-    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool):
+    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool):
         ld = (R + 7) // 8 * 8
+        q8 = mma and not small  # the fused GEMM takes INT8 codes; the decode GEMV is faster on the packed form
         self.pro = ops.PrologueOut(
-            a_pack=None if mma else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
-            a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if mma else None,
+            a_pack=None if q8 else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
+            a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=device) if (mma and R) else None,
             tail_rec=torch.empty(((M + 127) // 128, K // 128, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
             if (mma and R) else None,
@@ -69,7 +70,8 @@ class SplitLinear:
     def workspace(self, M: int) -> _Workspace:
         ws = self._ws.get(M)
         if ws is None:
-            ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M))
+            ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M),
+                                          M <= self.small_m)
         return ws
 
     def _pick_split_k(self, M: int) -> int:
@@ -94,15 +96,17 @@ class SplitLinear:
         if self._use_mma(M):
             return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot, pro=pro,
                                       R=self.R, bias=w.bias)
-        if self.R:
-            ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
-        if M <= self.small_m:
+        if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
+            if self.R:
+                ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
             if ws.acc is None:
                 ws.acc = torch.empty((M, self.N), dtype=torch.int32, device=ws.out.device)
-            ops.matmul_splitk(pro.a_pack, w.b_col, ws.acc, self._pick_split_k(M))
+            ops.gemv_splitk(pro.a_pack, w.b_col, ws.acc, self.split_k)
             ops.dequant_finish(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
-        else:
-            ops.split_gemm_fused(pro.a_pack, pro.body_scale, w.b_col, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
+            return ws.out
+        if self.R:
+            ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
+        ops.split_gemm_fused(pro.a_pack, pro.body_scale, w.b_col, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
         return ws.out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -318,6 +318,39 @@ def dequant_finish(C, body_scale, w_scale, out, tail=None, bias=None):
     return out
 
 
+def gemv_splitk(A, B_pack, C: torch.Tensor, split_k: int = 0) -> torch.Tensor:
+    """Decode path (M <= 64): exact INT4 x INT4 -> int32 with the weights streamed once; C is zeroed by the
+    call; split_k < 1 lets the library choose.  A is the packed uint8 [M,K/2] or the prologue's int8 [M,K]."""
+    _check_cuda(A, "A")
+    _check_cuda(B_pack, "B_pack", torch.uint8)
+    _check(A.dtype in (torch.uint8, torch.int8) and A.dim() == 2, "A must be uint8 [M,K/2] or int8 [M,K]")
+    a8 = A.dtype == torch.int8
+    M, N, K = A.shape[0], B_pack.shape[0], B_pack.shape[1] * 2
+    _check(A.shape[1] == (K if a8 else K // 2), "A and B_pack disagree on K")
+    _check_cuda(C, "C", torch.int32)
+    _check(C.numel() >= M * N, "C too small")
+    rc = _lib.load().tq_int4_gemv_splitk(None if a8 else _ptr(A), _ptr(A) if a8 else None, _ptr(B_pack), _ptr(C), M, N,
+                                         K, int(split_k), _stream())
+    _lib.check(rc, f"gemv_splitk(M={M}, N={N}, K={K}, split_k={split_k})")
+    return C
+
+
+def tail_gather_small(tail_idx, tail_val, w_t, tail_out, R: int):
+    """Tail sums for few rows (decode): gathers only the needed weight rows; eight interleaved fp32 chains per
+    output combined pairwise in a fixed order."""
+    _check_cuda(tail_idx, "tail_idx", torch.int16)
+    _check_cuda(tail_val, "tail_val", torch.bfloat16)
+    _check_cuda(w_t, "w_t", torch.bfloat16)
+    _check_cuda(tail_out, "tail_out", torch.float32)
+    M, ld = tail_idx.shape
+    K, N = w_t.shape
+    _check(tail_out.numel() >= M * N, "tail_out too small")
+    rc = _lib.load().tq_tail_gather_small(_ptr(tail_idx), _ptr(tail_val), _ptr(w_t), _ptr(tail_out), M, N, K, int(R),
+                                          ld, _stream())
+    _lib.check(rc, f"tail_gather_small(M={M}, N={N}, K={K}, R={R})")
+    return tail_out
+
+
 NOALLOC_MAX_ELEMS = 1 << 20  # TQ_NOALLOC_MAX_ELEMS of include/tailquant.h
 
 

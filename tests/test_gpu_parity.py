@@ -232,6 +232,43 @@ def test_tail_gather_bit_exact(M, N, K, R):
     assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("M,N,K,S", [(1, 4096, 4096, 0), (3, 72, 128, 1), (8, 520, 1024, 0), (16, 6144, 4096, 7),
+                                     (17, 1032, 4096, 0), (33, 64, 12288, 0), (64, 4096, 4096, 0),
+                                     (64, 264, 14336, 3), (48, 24576, 4096, 0)])
+def test_decode_gemv_bit_exact(M, N, K, S):
+    rng = np.random.default_rng(M + N + K + S)
+    qa, qw = rand_codes(rng, M, K), rand_codes(rng, N, K)
+    qa[0] = -8
+    qw[0] = -8
+    A = torch.from_numpy(O.pack_s4(qa)).cuda()
+    B = torch.from_numpy(O.pack_s4(qw)).cuda()
+    C = torch.full((M, N), 777, dtype=torch.int32, device="cuda")
+    ops.gemv_splitk(A, B, C, S)
+    assert np.array_equal(C.cpu().numpy(), O.int_gemm(qa, qw))
+    C.fill_(-5)
+    ops.gemv_splitk(torch.from_numpy(permute_q8(qa)).cuda(), B, C, S)  # INT8 activation operand
+    assert np.array_equal(C.cpu().numpy(), O.int_gemm(qa, qw))
+
+
+@pytest.mark.parametrize("M,N,K,R", [(1, 4096, 4096, 205), (5, 72, 512, 3), (64, 1032, 4096, 205), (9, 264, 12288, 615),
+                                     (2, 8, 128, 127)])
+def test_decode_tail_gather_bit_exact(M, N, K, R):
+    rng = np.random.default_rng(M + N + K + R)
+    idx = np.sort(np.argsort(rng.random((M, K)), axis=1)[:, :R], axis=1).astype(np.int32)
+    val = O.f32_to_bf16_bits(rng.standard_normal((M, R), dtype=np.float32) * 3)
+    w_rot = O.make_weights(N, K, seed=3)
+    ref = O.tail_t16_chains(idx, val, w_rot, 8)
+    ld = (R + 7) // 8 * 8
+    ti = np.zeros((M, ld), np.uint16)
+    tv = np.zeros((M, ld), np.uint16)
+    ti[:, :R] = idx
+    tv[:, :R] = val
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.tail_gather_small(torch.from_numpy(ti.view(np.int16)).cuda(), dev_bf16(tv),
+                          dev_bf16(np.ascontiguousarray(w_rot.T)), out, R)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+
+
 def _output_bounds(y_bits, y32, slack=0.0):
     """max-abs <= 2e-2 (or half an output ulp where that is larger, plus `slack` for a tail that was
     accumulated in another order) and mean-rel <= 1e-2 against the fp32 evaluation."""
@@ -369,7 +406,9 @@ def test_split_linear_end_to_end(M, K, N, kind, ratio, bias, engine):
     wb = O.make_weights(N, K, seed=1)
     b = np.random.default_rng(2).standard_normal(N, dtype=np.float32) if bias else None
     R = O.ceil_ratio_count(K, ratio)
-    yb_ref, y32, p, acc = O.split_linear_t16(xb, O.prepare_weight(wb, kind), kind, R, bias=b)
+    # M <= 64 takes the decode kernels, whose tail sum is eight interleaved chains
+    yb_ref, y32, p, acc = O.split_linear_t16(xb, O.prepare_weight(wb, kind), kind, R, bias=b,
+                                             tail_chains=8 if M <= 64 else 1)
     lin = SplitLinear(dev_bf16(wb), None if b is None else torch.from_numpy(b).cuda(), ratio=ratio, had_kind=kind,
                       tail_engine=engine)
     y = lin(dev_bf16(xb))
