@@ -4,6 +4,7 @@
 #include "tq_prologue.cu"
 #include "tq_gemm.cu"
 #include "tq_gemm_tail.cu"
+#include "tq_gemm_pair.cu"
 #include "tq_tail.cu"
 #include "tq_misc.cu"
 #include "tq_decode.cu"

@@ -1,0 +1,484 @@
+// Split GEMM on CTA pairs (sm_100a): the same computation as tq_gemm_tail.cu -- dense INT4 x INT4 part on tcgen05
+// kind::i8, tail as a bf16 tcgen05 product over the zero-filled tail tile, one fused epilogue -- but two CTAs of a
+// cluster share one 256 x 256 output tile: tcgen05.mma.cta_group::2 with M = 256.
+//
+// Why pairs: at M = 2048 these GEMMs are bound by the L2 -> SM bandwidth (see the profile summaries), and the B
+// operands dominate the traffic (INT4 weights + bf16 weight rows).  In a pair each CTA loads only ITS half of the
+// B tile (128 of the 256 output channels) and its own 128 rows of A; the tensor cores of both SMs read both
+// halves.  Per 128-wide K slice a CTA then loads 16 KB + 8 KB + 32 KB (+ 8 KB records) instead of
+// 16 KB + 16 KB + 64 KB (+ 8 KB).  Smaller slots also leave room for six of them.
+//
+// Protocol (rank 0 = leader issues every MMA):
+//   * every "slot full" barrier that the MMA issuer waits on lives in the LEADER; the other CTA's wideners and
+//     tail builders arrive on it through its shared::cluster address, and both CTAs' TMA loads count their bytes
+//     on it (cta_group::2 form of the tiled load; each CTA loads its own tiles, nothing is broadcast);
+//   * "slot empty" and "accumulator full" are signalled to both CTAs by one tcgen05.commit;
+//   * "accumulator empty" collects the epilogue threads of both CTAs in the leader;
+//   * tensor memory is allocated / freed by warp 1 of both CTAs with the cta_group::2 forms; the kernel starts
+//     and ends with a cluster-wide barrier so that no CTA touches a peer that has not started or has left.
+// Every mbarrier wait is bounded as in the one-CTA kernel.
+#include "tq_common.cuh"
+#include "tq_ptx.cuh"
+
+namespace tq {
+namespace {
+
+constexpr int P_BM = 128;  // rows of A per CTA (256 per pair)
+constexpr int P_BK = 128;
+constexpr int P_BUILD_WARPS = 8;
+constexpr int P_THREADS = (6 + P_BUILD_WARPS) * 32;
+
+struct PairGemmParams {
+  int M, N, K, R, ld, ptr_ld;
+  int tiles_m, tiles_n, kb_total, has_tail;
+  const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
+  const uint16_t* val;   // [M, ld] tail values
+  const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
+  const uint32_t* rec;   // [tiles_m][K/128][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
+  const uint16_t* cnt;   // [tiles_m][K/128][128]: entries of the row in the slice
+  const float* sx;
+  const float* sw;
+  const float* bias;
+  __nv_bfloat16* out;
+  int32_t* dbg_acc;   // optional [M,N]: the int32 accumulators
+  float* dbg_tail;    // optional [M,N]: the fp32 tail sums
+};
+
+constexpr int P_BN = 256;         // output channels per pair tile
+constexpr int P_BH = P_BN / 2;    // B rows (output channels) loaded by each CTA
+
+struct PS {
+  static constexpr int SU = 6;                            // operand slots
+  static constexpr int SP = 2;                            // packed-weight staging buffers
+  static constexpr int SLOT = (P_BM + P_BH) * 128;        // A region (16 KB) then this CTA's half of B (16 KB)
+  static constexpr int B_OFF = P_BM * 128;
+  static constexpr int STAGE = P_BH * (P_BK / 2);
+  static constexpr int STAGE_OFF = SU * SLOT;
+  static constexpr int BAR_OFF = STAGE_OFF + SP * STAGE;
+  static constexpr int NUM_BARS = 2 * SP + 2 * SU + 2;
+  static constexpr int DYN = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_constant__ CUtensorMap tmap_b4,
+                  const __grid_constant__ CUtensorMap tmap_w, const PairGemmParams p) {
+  using S = PS;
+  constexpr int BN = P_BN;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_dyn + (base - raw);
+
+  const uint32_t bars = base + S::BAR_OFF;
+  auto full_p = [&](int s) { return bars + 8u * s; };
+  auto empty_p = [&](int s) { return bars + 8u * (S::SP + s); };
+  auto full_u = [&](int s) { return bars + 8u * (2 * S::SP + s); };
+  auto empty_u = [&](int s) { return bars + 8u * (2 * S::SP + S::SU + s); };
+  const uint32_t acc_full = bars + 8u * (2 * S::SP + 2 * S::SU);
+  const uint32_t acc_empty = acc_full + 8u;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + S::BAR_OFF + S::NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + S::BAR_OFF + S::NUM_BARS * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int total_tiles = p.tiles_m * p.tiles_n;    // 256 x 256 pair tiles
+  auto lead = [&](uint32_t bar) { return map_to_cta(bar, 0u); };  // the leader's barrier at this offset
+  const bool has_tail = p.has_tail != 0;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // int32 accumulator, then fp32 tail accumulator
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a8)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b4)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+    for (int s = 0; s < S::SP; ++s) {
+      mbar_init(full_p(s), 1);
+      mbar_init(empty_p(s), 4);
+    }
+    for (int s = 0; s < S::SU; ++s) {
+      mbar_init(full_u(s), 8 + 1);  // four warps of each CTA + the leader producer's expect_tx (leader's copy is used)
+      mbar_init(empty_u(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 256);  // epilogue threads of both CTAs (leader's copy is used)
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs have initialised their barriers before anyone arrives on a peer's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // slot use number q -> (slot, parity)
+  auto slot_of = [](int q) { return q % S::SU; };
+  auto par_of = [](int q) { return (uint32_t)((q / S::SU) & 1); };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int q = 0, sp = 0;
+      uint32_t php = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < total_tiles; t += npairs) {
+        const int mt = t % p.tiles_m, nt = t / p.tiles_m;
+        for (int kb = 0; kb < p.kb_total; ++kb) {
+          if (!(ok = mbar_wait(empty_p(sp), php ^ 1u, abort_flag, 0x1000u))) break;
+          mbar_arrive_expect_tx(full_p(sp), S::STAGE);
+          tma_load_2d(base + S::STAGE_OFF + sp * S::STAGE, &tmap_b4, kb * (P_BK / 2), nt * BN + (int)rank * P_BH, full_p(sp));
+          if (++sp == S::SP) {
+            sp = 0;
+            php ^= 1u;
+          }
+          {
+            const int s = slot_of(q);
+            if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x2000u))) break;
+            if (rank == 0) mbar_arrive_expect_tx(full_u(s), 2 * P_BM * 128);  // the A tiles of both CTAs
+            tma_load_2d_pair(base + s * S::SLOT, &tmap_a8, kb * P_BK, (2 * mt + (int)rank) * P_BM, lead(full_u(s)));
+            ++q;
+          }
+          if (has_tail) {
+            for (int h = 0; h < 2 && ok; ++h) {
+              const int s = slot_of(q);
+              if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x4000u))) break;
+              if (rank == 0) mbar_arrive_expect_tx(full_u(s), BN * 128);  // both halves of the bf16 B tile
+              tma_load_2d_pair(base + s * S::SLOT + S::B_OFF, &tmap_w, kb * P_BK + h * 64, nt * BN + (int)rank * P_BH,
+                               lead(full_u(s)));
+              ++q;
+            }
+            if (!ok) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc_i8 = make_idesc_i8<BN, 256>();
+      constexpr uint32_t idesc_bf = make_idesc_bf16<BN, 256>();
+      int q = 0;
+      uint32_t pha = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < total_tiles; t += npairs) {
+        if (!(ok = mbar_wait(acc_empty, pha ^ 1u, abort_flag, 0x8000u))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < p.kb_total && ok; ++kb) {
+          {
+            const int s = slot_of(q);
+            if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x10000u))) break;
+            tc_fence_after();
+            const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_i8_pair(tmem_base, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_i8,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit_pair(empty_u(s));
+            ++q;
+          }
+          if (has_tail) {
+            for (int h = 0; h < 2; ++h) {
+              const int s = slot_of(q);
+              if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x20000u))) break;
+              tc_fence_after();
+              const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                umma_bf16_pair(tmem_base + BN, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_bf,
+                          (kb > 0 || h > 0 || k > 0) ? 1u : 0u);
+              umma_commit_pair(empty_u(s));
+              ++q;
+            }
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(acc_full);
+        pha ^= 1u;
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ wideners + epilogue
+    // These four warps widen the INT4 weight tiles of a tile's K slices, then drain its accumulators.
+    // (The tensor memory holds one accumulator set, so the next tile's MMAs wait for the epilogue anyway.)
+    const int quad = warp & 3;
+    const int etid = threadIdx.x - 2 * 32;  // 0..127
+    uint32_t pha = 0;
+    bool ok = true;
+    int wq = 0, kbg = 0;
+    // INT4 -> INT8 (x16) of one weight tile: staging buffer (kbg mod SP) -> B region of slot use q
+    auto widen = [&](int q, int kbg_) -> bool {
+      const int s = slot_of(q), sp = kbg_ % S::SP;
+      const uint32_t php = (uint32_t)((kbg_ / S::SP) & 1);
+      if (!mbar_wait(full_p(sp), php, abort_flag, 0x80000u)) return false;
+      if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u)) return false;
+      tc_fence_after();
+      const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
+      unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
+#pragma unroll
+      for (int task = etid; task < P_BH * 4; task += 128) {
+        const int row = task >> 2, piece = task & 3;
+        const uint4 w = *reinterpret_cast<const uint4*>(src + row * (P_BK / 2) + piece * 16);
+        unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
+        uint4 lo, hi;
+        lo.x = (w.x << 4) & 0xf0f0f0f0u;
+        lo.y = w.x & 0xf0f0f0f0u;
+        lo.z = (w.y << 4) & 0xf0f0f0f0u;
+        lo.w = w.y & 0xf0f0f0f0u;
+        hi.x = (w.z << 4) & 0xf0f0f0f0u;
+        hi.y = w.z & 0xf0f0f0f0u;
+        hi.z = (w.w << 4) & 0xf0f0f0f0u;
+        hi.w = w.w & 0xf0f0f0f0u;
+        *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_cluster(lead(full_u(s)));
+        mbar_arrive(empty_p(sp));
+      }
+      return true;
+    };
+    for (int t = pair; ok && t < total_tiles; t += npairs) {
+      const int mt = t % p.tiles_m, nt = t / p.tiles_m;
+      for (int kb = 0; kb < p.kb_total && ok; ++kb, ++kbg) {
+        ok = widen(wq, kbg);
+        wq += has_tail ? 3 : 1;
+      }
+      if (!ok) break;
+      if (!(ok = mbar_wait(acc_full, pha, abort_flag, 0x40000u))) break;
+      tc_fence_after();
+      const int row = (2 * mt + (int)rank) * P_BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sx = row_ok ? p.sx[row] : 0.0f;
+      const size_t rowoff = (size_t)row * p.N;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t ri[32], rf[32];
+        __syncwarp();
+        tmem_ld32(lane_addr + (uint32_t)c0, ri);
+        if (has_tail) {
+          tmem_ld32(lane_addr + (uint32_t)(BN + c0), rf);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) rf[i] = 0u;
+        }
+        const int n0 = nt * BN + c0;
+        if (!row_ok || n0 >= p.N) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + 8 * j;
+          if (n < p.N) {
+            float d[8];
+            const float4 w0 = *reinterpret_cast<const float4*>(p.sw + n);
+            const float4 w1 = *reinterpret_cast<const float4*>(p.sw + n + 4);
+            const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float dense = __fmul_rn(__fmul_rn((float)((int)ri[8 * j + i] >> 4), sx), ws[i]);
+              d[i] = has_tail ? __fadd_rn(dense, __uint_as_float(rf[8 * j + i])) : dense;
+            }
+            if (p.bias) {
+              const float4 b0 = *reinterpret_cast<const float4*>(p.bias + n);
+              const float4 b1 = *reinterpret_cast<const float4*>(p.bias + n + 4);
+              const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], bs[i]);
+            }
+            uint4 o;
+            o.x = f32_to_bf16_bits(d[0]) | (f32_to_bf16_bits(d[1]) << 16);
+            o.y = f32_to_bf16_bits(d[2]) | (f32_to_bf16_bits(d[3]) << 16);
+            o.z = f32_to_bf16_bits(d[4]) | (f32_to_bf16_bits(d[5]) << 16);
+            o.w = f32_to_bf16_bits(d[6]) | (f32_to_bf16_bits(d[7]) << 16);
+            *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+            if (p.dbg_acc) {
+              *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n) =
+                  make_int4((int)ri[8 * j] >> 4, (int)ri[8 * j + 1] >> 4, (int)ri[8 * j + 2] >> 4, (int)ri[8 * j + 3] >> 4);
+              *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n + 4) =
+                  make_int4((int)ri[8 * j + 4] >> 4, (int)ri[8 * j + 5] >> 4, (int)ri[8 * j + 6] >> 4, (int)ri[8 * j + 7] >> 4);
+            }
+            if (p.dbg_tail) {
+              *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n) = make_uint4(rf[8 * j], rf[8 * j + 1], rf[8 * j + 2], rf[8 * j + 3]);
+              *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n + 4) = make_uint4(rf[8 * j + 4], rf[8 * j + 5], rf[8 * j + 6], rf[8 * j + 7]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(lead(acc_empty));
+      pha ^= 1u;
+    }
+  } else {
+    // ------------------------------------------------------------------ tail builders
+    // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
+    // bf16 tail tile of that half.  The row's entries of a slice come as one record column
+    // ([slice][j][row]: a warp reads 128 contiguous bytes per j), fetched two slices ahead; the record
+    // already holds the swizzled position of the value inside the 128-byte tile row.
+    if (has_tail) {
+      constexpr int C = TQ_TAIL_REC_CAP;
+      const int btid = threadIdx.x - 6 * 32;
+      const int brow = btid & 127, half = btid >> 7;
+      const uint32_t roff = (uint32_t)((brow >> 3) * 1024 + (brow & 7) * 128);
+      const uint32_t halfbit = (uint32_t)half << 6;
+      bool ok = true;
+      int q = 1 + half;
+      for (int t = pair; ok && t < total_tiles; t += npairs) {
+        const int mt = 2 * (t % p.tiles_m) + (int)rank;  // this CTA's 128-row tile
+        const int grow = mt * P_BM + brow;
+        const uint32_t* recb = p.rec + (size_t)mt * p.kb_total * C * 128 + brow;
+        const uint16_t* cntb = p.cnt + (size_t)mt * p.kb_total * 128 + brow;
+        auto fetch = [&](uint32_t(&r)[C], int& n, int kb) {
+          if (kb < p.kb_total) {
+            uint32_t n16;
+            asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 128));
+            n = (int)n16;
+#pragma unroll
+            for (int j = 0; j < C; ++j)
+              asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + ((size_t)kb * C + j) * 128));
+          } else {
+            n = 0;
+          }
+        };
+        auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {
+          const int s = slot_of(q);
+          if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u)) return false;
+          tc_fence_after();
+          unsigned char* arow = sm + s * S::SLOT + roff;
+          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
+#pragma unroll
+          for (int j = 0; j < C; ++j) {
+            if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
+              *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
+          }
+          if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
+            const size_t lrow = (size_t)grow;
+            const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+            const int lo = e0 + C, hi = e0 + n;  // list positions [lo, hi)
+            const int kb0 = kb * P_BK + 64 * half;
+            if ((p.ld & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.val)) & 15) == 0) {
+              const uint4* irow = reinterpret_cast<const uint4*>(p.idx + lrow * p.ld);
+              const uint4* vrow = reinterpret_cast<const uint4*>(p.val + lrow * p.ld);
+              for (int g8 = lo >> 3; g8 <= (hi - 1) >> 3; ++g8) {
+                const uint4 gi = __ldg(irow + g8), gv = __ldg(vrow + g8);
+                const uint32_t wi[4] = {gi.x, gi.y, gi.z, gi.w}, wv[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  const int e = g8 * 8 + u;
+                  const int c = (int)((wi[u >> 1] >> ((u & 1) * 16)) & 0xffffu) - kb0;
+                  if (e >= lo && e < hi && c >= 0 && c < 64)
+                    *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                        (uint16_t)(wv[u >> 1] >> ((u & 1) * 16));
+                }
+              }
+            } else {
+              for (int e = lo; e < hi; ++e) {
+                const int c = (int)__ldg(p.idx + lrow * p.ld + e) - kb0;
+                if (c >= 0 && c < 64)
+                  *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                      __ldg(p.val + lrow * p.ld + e);
+              }
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(lead(full_u(s)));
+          q += 3;
+          return true;
+        };
+        uint32_t ra[C], rb[C];
+        int na = 0, nb = 0;
+        fetch(ra, na, 0);
+        fetch(rb, nb, 1);
+        for (int kb = 0; kb < p.kb_total && ok; kb += 2) {
+          ok = fill(kb, ra, na);
+          if (!ok) break;
+          fetch(ra, na, kb + 2);
+          if (kb + 1 < p.kb_total) {
+            ok = fill(kb + 1, rb, nb);
+            if (!ok) break;
+            fetch(rb, nb, kb + 3);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();  // the peer's MMAs, arrivals and loads are done with this CTA's memory
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot, PairGemmParams p, cudaStream_t st) {
+  using S = PS;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(dev < 64 && configured[dev])) {
+    cudaError_t e = cudaFuncSetAttribute(pair_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return TQ_ERR_CUDA;
+    }
+    if (dev < 64) configured[dev] = true;
+  }
+  CUtensorMap ma, mb, mw;
+  if (!make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_q8, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)p.K, 128,
+                          P_BM, true))
+    return TQ_ERR_CUDA;
+  if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_col, (uint64_t)(p.K / 2), (uint64_t)p.N,
+                          (uint64_t)(p.K / 2), P_BK / 2, P_BH))
+    return TQ_ERR_CUDA;
+  const void* wsrc = p.has_tail ? w_rot : (const void*)b_col;  // never loaded without a tail; kept valid
+  if (!make_tensor_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, wsrc, (uint64_t)(p.has_tail ? p.K : p.K / 4),
+                          (uint64_t)p.N, (uint64_t)(p.has_tail ? p.K * 2 : p.K / 2), 64, P_BH, true))
+    return TQ_ERR_CUDA;
+  p.tiles_m = (p.M + 2 * P_BM - 1) / (2 * P_BM);
+  p.tiles_n = (p.N + P_BN - 1) / P_BN;
+  p.kb_total = p.K / P_BK;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int total = p.tiles_m * p.tiles_n;
+  const int pairs = total < sms / 2 ? total : sms / 2;
+  pair_gemm_kernel<<<2 * pairs, P_THREADS, S::DYN, st>>>(ma, mb, mw, p);
+  return check_launch();
+}
+
+}  // namespace
+
+// Runs the pair kernel when the problem has enough 256 x 256 tiles to fill the machine; `*used` says whether it did.
+int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
+                  const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
+                  const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
+                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K,
+                  cudaStream_t st) {
+  PairGemmParams p = {};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.R = R;
+  p.ld = tail_ld;
+  p.ptr_ld = ptr_ld;
+  p.ptr = tail_ptr;
+  p.rec = tail_rec;
+  p.cnt = tail_cnt;
+  p.has_tail = R > 0 ? 1 : 0;
+  p.idx = tail_idx16;
+  p.val = reinterpret_cast<const uint16_t*>(tail_val);
+  p.sx = body_scale;
+  p.sw = w_scale;
+  p.bias = bias;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  p.dbg_acc = dbg_acc;
+  p.dbg_tail = dbg_tail;
+  return launch_pair_gemm(a_q8, b_col, w_rot, p, st);
+}
+
+}  // namespace tq

@@ -15,8 +15,9 @@
 //   bf16  (64 k) x2  tail values scattered by the builder warps   rotated bf16 weight rows [N,K], TMA
 //                    from the rows' (index, value) lists into a    (128-byte swizzle) straight into the slot
 //                    zero-filled tile
-// Warp roles: 0 = TMA producer, 1 = MMA issuer (+ tensor-memory allocation), 2..5 = weight wideners during
-// the main loop and epilogue at the end of the tile, 6..13 = tail-tile builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory, issued per CTA.
+// Warp roles: 0 = TMA producer of the INT8 path, 14 = TMA producer of the bf16 weight rows, 1 = MMA issuer
+// (+ tensor-memory allocation), 2..5 = weight wideners during the main loop and epilogue at the end of the
+// tile, 6..13 = tail-tile builders.  All loads are plain 2-D tiled TMA loads of this GPU's own memory, issued per CTA.
 // Every mbarrier wait is bounded (see mbar_wait).
 //
 // The activation codes arrive as INT8 with the two nibble planes of each 8-element group de-interleaved
@@ -28,17 +29,34 @@
 // Reference behaviour covered: GEMM + dequant + sparse correction in one kernel, i.e. what the reference
 // prototypes in tools/quarot_split_fused_epilogue_ext_v1.py:283-432 and
 // tools/qfactory_split_fused_epilogue_v1.py:153-233 (there with an INT4 tail and R fixed at compile time).
+#include <cstdlib>
+
 #include "tq_common.cuh"
 #include "tq_ptx.cuh"
 
 namespace tq {
 namespace {
 
+// Diagnostic build (-DTQ_GEMM_PROFILE): cycles each role spends in its barrier waits, summed over CTAs, in
+// g_wait_cycles[code]; read back with tq_gemm_wait_cycles().  Compiled out otherwise.
+#ifdef TQ_GEMM_PROFILE
+__device__ unsigned long long g_wait_cycles[16];
+#define TQ_WAIT(slot, call)                                                        \
+  [&]() -> bool {                                                                  \
+    const long long t0_ = clock64();                                               \
+    const bool r_ = (call);                                                        \
+    atomicAdd(&g_wait_cycles[slot], (unsigned long long)(clock64() - t0_));        \
+    return r_;                                                                     \
+  }()
+#else
+#define TQ_WAIT(slot, call) (call)
+#endif
+
 constexpr int G_BM = 128;
 constexpr int G_BK = 128;
 constexpr int G_BUILD_WARPS = 8;
 constexpr int G_NBT = G_BUILD_WARPS * 32;  // builder threads
-constexpr int G_THREADS = (6 + G_BUILD_WARPS) * 32;
+constexpr int G_THREADS = (6 + G_BUILD_WARPS + 1) * 32;  // + the warp of the second TMA producer
 constexpr int G_SENT = 0x7fffffff;
 
 struct SplitGemmParams {
@@ -125,8 +143,47 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
   auto slot_of = [](int q) { return q % S::SU; };
   auto par_of = [](int q) { return (uint32_t)((q / S::SU) & 1); };
 
+  // INT4 -> INT8 (x16) of one weight tile by four warps (wtid = 0..127): staging buffer (kbg mod SP) -> B region
+  // of slot use q
+  auto widen = [&](int q, int kbg_, int wtid) -> bool {
+    const int s = slot_of(q), sp = kbg_ % S::SP;
+    const uint32_t php = (uint32_t)((kbg_ / S::SP) & 1);
+    if (!TQ_WAIT(7, mbar_wait(full_p(sp), php, abort_flag, 0x80000u))) return false;
+    if (!TQ_WAIT(8, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u))) return false;
+    tc_fence_after();
+    const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
+    unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
+#pragma unroll
+    for (int task = wtid; task < BN * 4; task += 128) {
+      const int row = task >> 2, piece = task & 3;
+      const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
+      unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
+      uint4 lo, hi;
+      lo.x = (w.x << 4) & 0xf0f0f0f0u;
+      lo.y = w.x & 0xf0f0f0f0u;
+      lo.z = (w.y << 4) & 0xf0f0f0f0u;
+      lo.w = w.y & 0xf0f0f0f0u;
+      hi.x = (w.z << 4) & 0xf0f0f0f0u;
+      hi.y = w.z & 0xf0f0f0f0u;
+      hi.z = (w.w << 4) & 0xf0f0f0f0u;
+      hi.w = w.w & 0xf0f0f0f0u;
+      *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(full_u(s));
+      mbar_arrive(empty_p(sp));
+    }
+    return true;
+  };
+
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer, INT8 path
+    // (packed INT4 weights -> staging, INT8 activations -> slot).  The bf16 weight rows have their own producer
+    // (last warp): a producer blocks on the slot it is about to fill, and with a single one a busy bf16 slot
+    // held back the next packed-weight load although its staging buffer was free.
     if (lane == 0) {
       int q = 0, sp = 0;
       uint32_t php = 0;
@@ -134,30 +191,36 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         const int mt = t % p.tiles_m, nt = t / p.tiles_m;
         for (int kb = 0; kb < p.kb_total; ++kb) {
-          if (!(ok = mbar_wait(empty_p(sp), php ^ 1u, abort_flag, 0x1000u))) break;
+          if (!(ok = TQ_WAIT(0, mbar_wait(empty_p(sp), php ^ 1u, abort_flag, 0x1000u)))) break;
           mbar_arrive_expect_tx(full_p(sp), S::STAGE);
           tma_load_2d(base + S::STAGE_OFF + sp * S::STAGE, &tmap_b4, kb * (G_BK / 2), nt * BN, full_p(sp));
           if (++sp == S::SP) {
             sp = 0;
             php ^= 1u;
           }
-          {
-            const int s = slot_of(q);
-            if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x2000u))) break;
-            mbar_arrive_expect_tx(full_u(s), G_BM * 128);
-            tma_load_2d(base + s * S::SLOT, &tmap_a8, kb * G_BK, mt * G_BM, full_u(s));
-            ++q;
+          const int s = slot_of(q);
+          if (!(ok = TQ_WAIT(1, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x2000u)))) break;
+          mbar_arrive_expect_tx(full_u(s), G_BM * 128);
+          tma_load_2d(base + s * S::SLOT, &tmap_a8, kb * G_BK, mt * G_BM, full_u(s));
+          q += has_tail ? 3 : 1;
+        }
+      }
+    }
+  } else if (warp == 6 + G_BUILD_WARPS) {
+    // ------------------------------------------------------------------ TMA producer, bf16 weight rows
+    if (lane == 0 && has_tail) {
+      int q = 1;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const int nt = t / p.tiles_m;
+        for (int kb = 0; kb < p.kb_total && ok; ++kb) {
+          for (int h = 0; h < 2; ++h) {
+            const int s = slot_of(q + h);
+            if (!(ok = TQ_WAIT(2, mbar_wait(empty_u(s), par_of(q + h) ^ 1u, abort_flag, 0x4000u)))) break;
+            mbar_arrive_expect_tx(full_u(s), BN * 128);
+            tma_load_2d(base + s * S::SLOT + S::B_OFF, &tmap_w, kb * G_BK + h * 64, nt * BN, full_u(s));
           }
-          if (has_tail) {
-            for (int h = 0; h < 2 && ok; ++h) {
-              const int s = slot_of(q);
-              if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x4000u))) break;
-              mbar_arrive_expect_tx(full_u(s), BN * 128);
-              tma_load_2d(base + s * S::SLOT + S::B_OFF, &tmap_w, kb * G_BK + h * 64, nt * BN, full_u(s));
-              ++q;
-            }
-            if (!ok) break;
-          }
+          q += 3;
         }
       }
     }
@@ -170,12 +233,12 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
       uint32_t pha = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        if (!(ok = mbar_wait(acc_empty, pha ^ 1u, abort_flag, 0x8000u))) break;
+        if (!(ok = TQ_WAIT(3, mbar_wait(acc_empty, pha ^ 1u, abort_flag, 0x8000u)))) break;
         tc_fence_after();
         for (int kb = 0; kb < p.kb_total && ok; ++kb) {
           {
             const int s = slot_of(q);
-            if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x10000u))) break;
+            if (!(ok = TQ_WAIT(4, mbar_wait(full_u(s), par_of(q), abort_flag, 0x10000u)))) break;
             tc_fence_after();
             const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
 #pragma unroll
@@ -188,7 +251,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
           if (has_tail) {
             for (int h = 0; h < 2; ++h) {
               const int s = slot_of(q);
-              if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x20000u))) break;
+              if (!(ok = TQ_WAIT(5, mbar_wait(full_u(s), par_of(q), abort_flag, 0x20000u)))) break;
               tc_fence_after();
               const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
 #pragma unroll
@@ -214,48 +277,14 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
     uint32_t pha = 0;
     bool ok = true;
     int wq = 0, kbg = 0;
-    // INT4 -> INT8 (x16) of one weight tile: staging buffer (kbg mod SP) -> B region of slot use q
-    auto widen = [&](int q, int kbg_) -> bool {
-      const int s = slot_of(q), sp = kbg_ % S::SP;
-      const uint32_t php = (uint32_t)((kbg_ / S::SP) & 1);
-      if (!mbar_wait(full_p(sp), php, abort_flag, 0x80000u)) return false;
-      if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u)) return false;
-      tc_fence_after();
-      const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
-      unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
-#pragma unroll
-      for (int task = etid; task < BN * 4; task += 128) {
-        const int row = task >> 2, piece = task & 3;
-        const uint4 w = *reinterpret_cast<const uint4*>(src + row * (G_BK / 2) + piece * 16);
-        unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
-        uint4 lo, hi;
-        lo.x = (w.x << 4) & 0xf0f0f0f0u;
-        lo.y = w.x & 0xf0f0f0f0u;
-        lo.z = (w.y << 4) & 0xf0f0f0f0u;
-        lo.w = w.y & 0xf0f0f0f0u;
-        hi.x = (w.z << 4) & 0xf0f0f0f0u;
-        hi.y = w.z & 0xf0f0f0f0u;
-        hi.z = (w.w << 4) & 0xf0f0f0f0u;
-        hi.w = w.w & 0xf0f0f0f0u;
-        *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(full_u(s));
-        mbar_arrive(empty_p(sp));
-      }
-      return true;
-    };
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       const int mt = t % p.tiles_m, nt = t / p.tiles_m;
       for (int kb = 0; kb < p.kb_total && ok; ++kb, ++kbg) {
-        ok = widen(wq, kbg);
+        ok = widen(wq, kbg, etid);
         wq += has_tail ? 3 : 1;
       }
       if (!ok) break;
-      if (!(ok = mbar_wait(acc_full, pha, abort_flag, 0x40000u))) break;
+      if (!(ok = TQ_WAIT(6, mbar_wait(acc_full, pha, abort_flag, 0x40000u)))) break;
       tc_fence_after();
       const int row = mt * G_BM + quad * 32 + lane;
       const bool row_ok = row < p.M;
@@ -318,7 +347,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
       mbar_arrive(acc_empty);
       pha ^= 1u;
     }
-  } else {
+  } else if (warp < 6 + G_BUILD_WARPS) {
     // ------------------------------------------------------------------ tail builders
     // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
     // bf16 tail tile of that half.  The row's entries of a slice come as one record column
@@ -351,7 +380,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
         };
         auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {
           const int s = slot_of(q);
-          if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u)) return false;
+          if (!TQ_WAIT(9, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u))) return false;
           tc_fence_after();
           unsigned char* arow = sm + s * S::SLOT + roff;
           const uint4 z = make_uint4(0u, 0u, 0u, 0u);
@@ -464,6 +493,37 @@ int launch_split_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_ro
 }  // namespace
 }  // namespace tq
 
+namespace tq {
+// -1 = default (one-CTA kernel), 0 = one-CTA kernel, 1 = CTA-pair kernel (initial value from TQ_GEMM_PAIR)
+static int g_gemm_pair_mode = [] {
+  const char* e = getenv("TQ_GEMM_PAIR");
+  return e ? atoi(e) : -1;
+}();
+int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
+                  const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
+                  const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
+                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K,
+                  cudaStream_t st);
+}
+
+#ifdef TQ_GEMM_PROFILE
+extern "C" int tq_gemm_wait_cycles(unsigned long long* out16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, tq::g_wait_cycles, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {};
+    cudaMemcpyToSymbol(tq::g_wait_cycles, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
+extern "C" int tq_set_gemm_pair_mode(int mode) {
+  if (mode < -1 || mode > 1) return TQ_ERR_BAD_ARG;
+  tq::g_gemm_pair_mode = mode;
+  return TQ_OK;
+}
+
 extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                                  const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
                                  const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
@@ -482,6 +542,13 @@ extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, co
       (dbg_tail && !aligned16(dbg_tail)))
     return TQ_ERR_MISALIGNED;
   if (M == 0) return TQ_OK;
+  {
+    // The CTA-pair kernel (256 x 256 tiles, half the B traffic per CTA) measured 8-25 % slower than the one-CTA
+    // kernel on every shape tried, so it runs only when asked for (TQ_GEMM_PAIR=1 or tq_set_gemm_pair_mode(1)).
+    if (g_gemm_pair_mode == 1)
+      return run_pair_gemm(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld,
+                           tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, (cudaStream_t)stream);
+  }
   SplitGemmParams p = {};
   p.M = M;
   p.N = N;

@@ -308,6 +308,11 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
     return out
 
 
+def set_gemm_pair_mode(mode: int) -> None:
+    """-1: split_gemm_mma picks its kernel by problem size; 0: one CTA per tile; 1: CTA pairs (256 x 256 tiles)."""
+    _lib.check(_lib.load().tq_set_gemm_pair_mode(int(mode)), "set_gemm_pair_mode")
+
+
 def dequant_finish(C, body_scale, w_scale, out, tail=None, bias=None):
     _check_cuda(C, "C", torch.int32)
     M, N = C.shape

@@ -332,7 +332,8 @@ def test_prologue_int8_operand(kind, K, M, R):
                                                   (129, 136, 12288, 615, True, False),
                                                   (2048, 512, 256, 13, False, False), (1, 8, 128, 3, False, False),
                                                   (140, 264, 1024, 205, False, True)])
-def test_split_gemm_mma(M, N, K, R, bias, cluster):
+@pytest.mark.parametrize("pair", [0, 1])
+def test_split_gemm_mma(M, N, K, R, bias, cluster, pair):
     """Fused kernel: int32 accumulators bit-exact, tensor-core tail within fp32 accumulation error of the
     fixed-order chain, bf16 output within the stated bounds."""
     rng = np.random.default_rng(M + N + K + R)
@@ -371,9 +372,13 @@ def test_split_gemm_mma(M, N, K, R, bias, cluster):
     out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     dacc = torch.empty((M, N), dtype=torch.int32, device="cuda")
     dtail = torch.empty((M, N), dtype=torch.float32, device="cuda")
-    ops.split_gemm_mma(g(permute_q8(qa)), g(sx), g(O.pack_s4(qw)), g(sw), out, w_rot=dev_bf16(w_rot), pro=pro, R=R,
-                       bias=None if b is None else g(b),
-                       dbg_acc=dacc, dbg_tail=dtail)
+    ops.set_gemm_pair_mode(pair)  # both kernels of the fused GEMM: one CTA per tile, CTA pairs
+    try:
+        ops.split_gemm_mma(g(permute_q8(qa)), g(sx), g(O.pack_s4(qw)), g(sw), out, w_rot=dev_bf16(w_rot), pro=pro, R=R,
+                           bias=None if b is None else g(b), dbg_acc=dacc, dbg_tail=dtail)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_gemm_pair_mode(-1)
     assert np.array_equal(dacc.cpu().numpy(), acc), "int32 accumulators"
     slack = 0.0
     if R:
