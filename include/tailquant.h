@@ -157,9 +157,9 @@ int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t
                       int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream);
 
 /* tq_split_gemm_mma has two kernels: one CTA per 128 x 256 tile, and CTA pairs on 256 x 256 tiles
- * (tcgen05 cta_group::2; each CTA loads half of the weight tiles).  mode -1 is the default choice (the one-CTA
- * kernel, the faster of the two on every measured shape), 0 / 1 force one of them.  A tuning knob without a
- * reference counterpart. */
+ * (tcgen05 cta_group::2; each CTA loads half of the weight tiles).  mode -1 (default) chooses by shape (pairs
+ * without a tail, and with a tail for K < 8192 and M <= 4096), 0 / 1 force one of them.  A tuning knob without
+ * a reference counterpart. */
 int tq_set_gemm_pair_mode(int mode);
 
 /* Finisher of the split-K path: out = bf16((float(C)*body_scale[m])*w_scale[n] + tail + bias). */

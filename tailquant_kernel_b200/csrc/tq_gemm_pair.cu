@@ -26,7 +26,10 @@ namespace {
 constexpr int P_BM = 128;  // rows of A per CTA (256 per pair)
 constexpr int P_BK = 128;
 constexpr int P_BUILD_WARPS = 8;
-constexpr int P_THREADS = (6 + P_BUILD_WARPS) * 32;
+// warp 0: packed-weight producer, 1: MMA issuer, 2..5: wideners, 6..13: tail builders, 14: INT8 activation
+// producer, 15: bf16 weight-row producer.  Warps 2..13 share the epilogue.
+constexpr int P_THREADS = (6 + P_BUILD_WARPS + 2) * 32;
+constexpr int P_LOOK = 2;  // K slices of the next tile prepared before a tile's epilogue
 
 struct PairGemmParams {
   int M, N, K, R, ld, ptr_ld;
@@ -49,7 +52,7 @@ constexpr int P_BH = P_BN / 2;    // B rows (output channels) loaded by each CTA
 
 struct PS {
   static constexpr int SU = 6;                            // operand slots
-  static constexpr int SP = 2;                            // packed-weight staging buffers
+  static constexpr int SP = 4;                            // packed-weight staging buffers
   static constexpr int SLOT = (P_BM + P_BH) * 128;        // A region (16 KB) then this CTA's half of B (16 KB)
   static constexpr int B_OFF = P_BM * 128;
   static constexpr int STAGE = P_BH * (P_BK / 2);
@@ -58,6 +61,12 @@ struct PS {
   static constexpr int NUM_BARS = 2 * SP + 2 * SU + 2;
   static constexpr int DYN = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
 };
+static_assert(PS::DYN <= 232448, "shared memory of the pair kernel");
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_constant__ CUtensorMap tmap_b4,
@@ -83,8 +92,13 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
   const int total_tiles = p.tiles_m * p.tiles_n;    // 256 x 256 pair tiles
+  const int my_tiles = pair < total_tiles ? (total_tiles - pair + npairs - 1) / npairs : 0;  // tiles pair, pair + npairs, ...
+  const int kbt = p.kb_total;
+  const int G = my_tiles * kbt;                     // K slices this pair goes through, over all its tiles
+  const int look = kbt < P_LOOK ? kbt : P_LOOK;
   auto lead = [&](uint32_t bar) { return map_to_cta(bar, 0u); };  // the leader's barrier at this offset
   const bool has_tail = p.has_tail != 0;
+  const int uses = has_tail ? 3 : 1;                // slot uses per K slice: INT8 operands, then two bf16 halves
   constexpr uint32_t TMEM_COLS = 2 * BN;  // int32 accumulator, then fp32 tail accumulator
 
   if (threadIdx.x == 0) {
@@ -100,7 +114,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       mbar_init(empty_u(s), 1);
     }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 256);  // epilogue threads of both CTAs (leader's copy is used)
+    mbar_init(acc_empty, 2 * (4 + P_BUILD_WARPS));  // the epilogue warps of both CTAs (leader's copy is used)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -116,41 +130,172 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
   // slot use number q -> (slot, parity)
   auto slot_of = [](int q) { return q % S::SU; };
   auto par_of = [](int q) { return (uint32_t)((q / S::SU) & 1); };
+  // local tile number i -> tile coordinates
+  auto tile_mt = [&](int i) { return (pair + i * npairs) % p.tiles_m; };
+  auto tile_nt = [&](int i) { return (pair + i * npairs) / p.tiles_m; };
+
+  // Epilogue share of one warp (2..13) for local tile i: column chunks [c_lo, c_hi) of 32 channels each, rows of
+  // the warp's tensor-memory lane quadrant.  y = bf16((float(acc) * s_x) * s_w + tail + bias).
+  auto epilogue = [&](int i, int c_lo, int c_hi) -> bool {
+    if (!TQ_WAIT(6, mbar_wait(acc_full, (uint32_t)(i & 1), abort_flag, 0x40000u))) return false;
+    tc_fence_after();
+    const int mt = tile_mt(i), nt = tile_nt(i);
+    const int quad = warp & 3;
+    const int row = (2 * mt + (int)rank) * P_BM + quad * 32 + lane;
+    const bool row_ok = row < p.M;
+    const float sx = row_ok ? p.sx[row] : 0.0f;
+    const size_t rowoff = (size_t)row * p.N;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+    for (int c = c_lo; c < c_hi; ++c) {
+      const int c0 = c * 32;
+      uint32_t ri[32], rf[32];
+      __syncwarp();
+      tmem_ld32(lane_addr + (uint32_t)c0, ri);
+      if (has_tail) {
+        tmem_ld32(lane_addr + (uint32_t)(BN + c0), rf);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) rf[k] = 0u;
+      }
+      const int n0 = nt * BN + c0;
+      if (!row_ok || n0 >= p.N) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + 8 * j;
+        if (n < p.N) {
+          float d[8];
+          const float4 w0 = *reinterpret_cast<const float4*>(p.sw + n);
+          const float4 w1 = *reinterpret_cast<const float4*>(p.sw + n + 4);
+          const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float dense = __fmul_rn(__fmul_rn((float)((int)ri[8 * j + k] >> 4), sx), ws[k]);
+            d[k] = has_tail ? __fadd_rn(dense, __uint_as_float(rf[8 * j + k])) : dense;
+          }
+          if (p.bias) {
+            const float4 b0 = *reinterpret_cast<const float4*>(p.bias + n);
+            const float4 b1 = *reinterpret_cast<const float4*>(p.bias + n + 4);
+            const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) d[k] = __fadd_rn(d[k], bs[k]);
+          }
+          uint4 o;
+          o.x = pack_bf16x2(d[0], d[1]);
+          o.y = pack_bf16x2(d[2], d[3]);
+          o.z = pack_bf16x2(d[4], d[5]);
+          o.w = pack_bf16x2(d[6], d[7]);
+          *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+          if (p.dbg_acc) {
+            *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n) =
+                make_int4((int)ri[8 * j] >> 4, (int)ri[8 * j + 1] >> 4, (int)ri[8 * j + 2] >> 4, (int)ri[8 * j + 3] >> 4);
+            *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n + 4) =
+                make_int4((int)ri[8 * j + 4] >> 4, (int)ri[8 * j + 5] >> 4, (int)ri[8 * j + 6] >> 4, (int)ri[8 * j + 7] >> 4);
+          }
+          if (p.dbg_tail) {
+            *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n) = make_uint4(rf[8 * j], rf[8 * j + 1], rf[8 * j + 2], rf[8 * j + 3]);
+            *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n + 4) = make_uint4(rf[8 * j + 4], rf[8 * j + 5], rf[8 * j + 6], rf[8 * j + 7]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(lead(acc_empty));
+    return true;
+  };
+  // the eight 32-channel chunks of a tile are split 3 / 3 / 2 over the three warps of a lane quadrant
+  const int ethird = (warp - 2) >> 2;
+  const int c_lo = ethird * 3, c_hi = ethird == 2 ? 8 : ethird * 3 + 3;
+  bool ok = true;
+  int epi_done = 0;  // tiles whose epilogue share this warp has done
+  auto catch_up = [&](int upto) {
+    while (ok && epi_done < upto) ok = epilogue(epi_done++, c_lo, c_hi);
+  };
+  // INT4 -> INT8 (x16) of K slice g's weight tile by four warps (wtid = 0..127): staging buffer -> B region of
+  // the slice's INT8 slot.  One group of four warps sees every phase of the staging barriers it waits on.
+  auto widen_one = [&](int g, int wtid) -> bool {
+    const int q = g * uses, s = slot_of(q), sp = g % S::SP;
+    const uint32_t php = (uint32_t)((g / S::SP) & 1);
+    if (wtid == 0) TQ_TRACE(3, q, 0);
+    if (!TQ_WAIT(7, mbar_wait(full_p(sp), php, abort_flag, 0x80000u))) return false;
+    if (wtid == 0) TQ_TRACE(3, q, 1);
+    if (!TQ_WAIT(8, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u))) return false;
+    if (wtid == 0) TQ_TRACE(3, q, 2);
+    tc_fence_after();
+    const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
+    unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
+#pragma unroll
+    for (int task = wtid; task < P_BH * 4; task += 128) {
+      const int row = task >> 2, piece = task & 3;
+      const uint4 w = *reinterpret_cast<const uint4*>(src + row * (P_BK / 2) + piece * 16);
+      unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
+      uint4 lo, hi;
+      lo.x = (w.x << 4) & 0xf0f0f0f0u;
+      lo.y = w.x & 0xf0f0f0f0u;
+      lo.z = (w.y << 4) & 0xf0f0f0f0u;
+      lo.w = w.y & 0xf0f0f0f0u;
+      hi.x = (w.z << 4) & 0xf0f0f0f0u;
+      hi.y = w.z & 0xf0f0f0f0u;
+      hi.z = (w.w << 4) & 0xf0f0f0f0u;
+      hi.w = w.w & 0xf0f0f0f0u;
+      *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive_cluster(lead(full_u(s)));
+      mbar_arrive(empty_p(sp));
+    }
+    if (wtid == 0) TQ_TRACE(3, q, 3);
+    return true;
+  };
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer: packed INT4 weights
     if (lane == 0) {
-      int q = 0, sp = 0;
-      uint32_t php = 0;
+      for (int g = 0; g < G; ++g) {
+        const int sp = g % S::SP;
+        const uint32_t php = (uint32_t)((g / S::SP) & 1);
+        TQ_TRACE(6, g * uses, 0);
+        if (!TQ_WAIT(0, mbar_wait(empty_p(sp), php ^ 1u, abort_flag, 0x1000u))) break;
+        TQ_TRACE(6, g * uses, 1);
+        const int i = g / kbt, kb = g - i * kbt;
+        mbar_arrive_expect_tx(full_p(sp), S::STAGE);
+        tma_load_2d(base + S::STAGE_OFF + sp * S::STAGE, &tmap_b4, kb * (P_BK / 2), tile_nt(i) * BN + (int)rank * P_BH,
+                    full_p(sp));
+      }
+    }
+  } else if (warp == 6 + P_BUILD_WARPS) {
+    // ------------------------------------------------------------------ TMA producer: INT8 activations
+    if (lane == 0) {
+      for (int g = 0; g < G; ++g) {
+        const int q = g * uses, s = slot_of(q);
+        TQ_TRACE(1, q, 0);
+        if (!TQ_WAIT(1, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x2000u))) break;
+        TQ_TRACE(1, q, 1);
+        const int i = g / kbt, kb = g - i * kbt;
+        if (rank == 0) mbar_arrive_expect_tx(full_u(s), 2 * P_BM * 128);  // the A tiles of both CTAs
+        tma_load_2d_pair(base + s * S::SLOT, &tmap_a8, kb * P_BK, (2 * tile_mt(i) + (int)rank) * P_BM, lead(full_u(s)));
+        TQ_TRACE(1, q, 2);
+      }
+    }
+  } else if (warp == 6 + P_BUILD_WARPS + 1) {
+    // ------------------------------------------------------------------ TMA producer: bf16 weight rows
+    if (lane == 0 && has_tail) {
       bool ok = true;
-      for (int t = pair; ok && t < total_tiles; t += npairs) {
-        const int mt = t % p.tiles_m, nt = t / p.tiles_m;
-        for (int kb = 0; kb < p.kb_total; ++kb) {
-          if (!(ok = mbar_wait(empty_p(sp), php ^ 1u, abort_flag, 0x1000u))) break;
-          mbar_arrive_expect_tx(full_p(sp), S::STAGE);
-          tma_load_2d(base + S::STAGE_OFF + sp * S::STAGE, &tmap_b4, kb * (P_BK / 2), nt * BN + (int)rank * P_BH, full_p(sp));
-          if (++sp == S::SP) {
-            sp = 0;
-            php ^= 1u;
-          }
-          {
-            const int s = slot_of(q);
-            if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x2000u))) break;
-            if (rank == 0) mbar_arrive_expect_tx(full_u(s), 2 * P_BM * 128);  // the A tiles of both CTAs
-            tma_load_2d_pair(base + s * S::SLOT, &tmap_a8, kb * P_BK, (2 * mt + (int)rank) * P_BM, lead(full_u(s)));
-            ++q;
-          }
-          if (has_tail) {
-            for (int h = 0; h < 2 && ok; ++h) {
-              const int s = slot_of(q);
-              if (!(ok = mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x4000u))) break;
-              if (rank == 0) mbar_arrive_expect_tx(full_u(s), BN * 128);  // both halves of the bf16 B tile
-              tma_load_2d_pair(base + s * S::SLOT + S::B_OFF, &tmap_w, kb * P_BK + h * 64, nt * BN + (int)rank * P_BH,
-                               lead(full_u(s)));
-              ++q;
-            }
-            if (!ok) break;
-          }
+      for (int g = 0; g < G && ok; ++g) {
+        const int i = g / kbt, kb = g - i * kbt;
+        const int nrow = tile_nt(i) * BN + (int)rank * P_BH;
+        for (int h = 0; h < 2; ++h) {
+          const int q = 3 * g + 1 + h, s = slot_of(q);
+          TQ_TRACE(2, q, 0);
+          if (!(ok = TQ_WAIT(2, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x4000u)))) break;
+          TQ_TRACE(2, q, 1);
+          if (rank == 0) mbar_arrive_expect_tx(full_u(s), BN * 128);  // both halves of the bf16 B tile
+          tma_load_2d_pair(base + s * S::SLOT + S::B_OFF, &tmap_w, kb * P_BK + h * 64, nrow, lead(full_u(s)));
+          TQ_TRACE(2, q, 2);
         }
       }
     }
@@ -160,15 +305,16 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       constexpr uint32_t idesc_i8 = make_idesc_i8<BN, 256>();
       constexpr uint32_t idesc_bf = make_idesc_bf16<BN, 256>();
       int q = 0;
-      uint32_t pha = 0;
       bool ok = true;
-      for (int t = pair; ok && t < total_tiles; t += npairs) {
-        if (!(ok = mbar_wait(acc_empty, pha ^ 1u, abort_flag, 0x8000u))) break;
+      for (int i = 0; ok && i < my_tiles; ++i) {
+        if (!(ok = TQ_WAIT(3, mbar_wait(acc_empty, (uint32_t)(i & 1) ^ 1u, abort_flag, 0x8000u)))) break;
         tc_fence_after();
-        for (int kb = 0; kb < p.kb_total && ok; ++kb) {
+        for (int kb = 0; kb < kbt && ok; ++kb) {
           {
             const int s = slot_of(q);
-            if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x10000u))) break;
+            TQ_TRACE(0, q, 0);
+            if (!(ok = TQ_WAIT(4, mbar_wait(full_u(s), par_of(q), abort_flag, 0x10000u)))) break;
+            TQ_TRACE(0, q, 1);
             tc_fence_after();
             const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
 #pragma unroll
@@ -176,12 +322,15 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
               umma_i8_pair(tmem_base, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_i8,
                       (kb > 0 || k > 0) ? 1u : 0u);
             umma_commit_pair(empty_u(s));
+            TQ_TRACE(0, q, 2);
             ++q;
           }
           if (has_tail) {
             for (int h = 0; h < 2; ++h) {
               const int s = slot_of(q);
-              if (!(ok = mbar_wait(full_u(s), par_of(q), abort_flag, 0x20000u))) break;
+              TQ_TRACE(0, q, 0);
+              if (!(ok = TQ_WAIT(5, mbar_wait(full_u(s), par_of(q), abort_flag, 0x20000u)))) break;
+              TQ_TRACE(0, q, 1);
               tc_fence_after();
               const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
 #pragma unroll
@@ -189,130 +338,31 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
                 umma_bf16_pair(tmem_base + BN, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_bf,
                           (kb > 0 || h > 0 || k > 0) ? 1u : 0u);
               umma_commit_pair(empty_u(s));
+              TQ_TRACE(0, q, 2);
               ++q;
             }
           }
         }
         if (!ok) break;
         umma_commit_pair(acc_full);
-        pha ^= 1u;
       }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------------ wideners + epilogue
-    // These four warps widen the INT4 weight tiles of a tile's K slices, then drain its accumulators.
-    // (The tensor memory holds one accumulator set, so the next tile's MMAs wait for the epilogue anyway.)
-    const int quad = warp & 3;
+    // ------------------------------------------------------------------ wideners (+ epilogue share)
+    // INT4 -> INT8 (x16) of the pair's weight tiles, one K slice after the other over all its tiles.  The
+    // epilogue of a tile is taken up once the first slices of the NEXT tile are widened, so that the MMAs
+    // restart as soon as the accumulators are drained.  Without a tail these warps take the even slices and
+    // four of the idle builder warps the odd ones.
     const int etid = threadIdx.x - 2 * 32;  // 0..127
-    uint32_t pha = 0;
-    bool ok = true;
-    int wq = 0, kbg = 0;
-    // INT4 -> INT8 (x16) of one weight tile: staging buffer (kbg mod SP) -> B region of slot use q
-    auto widen = [&](int q, int kbg_) -> bool {
-      const int s = slot_of(q), sp = kbg_ % S::SP;
-      const uint32_t php = (uint32_t)((kbg_ / S::SP) & 1);
-      if (!mbar_wait(full_p(sp), php, abort_flag, 0x80000u)) return false;
-      if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x100000u)) return false;
-      tc_fence_after();
-      const unsigned char* src = sm + S::STAGE_OFF + sp * S::STAGE;
-      unsigned char* dst = sm + s * S::SLOT + S::B_OFF;
-#pragma unroll
-      for (int task = etid; task < P_BH * 4; task += 128) {
-        const int row = task >> 2, piece = task & 3;
-        const uint4 w = *reinterpret_cast<const uint4*>(src + row * (P_BK / 2) + piece * 16);
-        unsigned char* drow = dst + (row >> 3) * 1024 + (row & 7) * 128;
-        uint4 lo, hi;
-        lo.x = (w.x << 4) & 0xf0f0f0f0u;
-        lo.y = w.x & 0xf0f0f0f0u;
-        lo.z = (w.y << 4) & 0xf0f0f0f0u;
-        lo.w = w.y & 0xf0f0f0f0u;
-        hi.x = (w.z << 4) & 0xf0f0f0f0u;
-        hi.y = w.z & 0xf0f0f0f0u;
-        hi.z = (w.w << 4) & 0xf0f0f0f0u;
-        hi.w = w.w & 0xf0f0f0f0u;
-        *reinterpret_cast<uint4*>(drow + (((2 * piece) ^ (row & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(drow + (((2 * piece + 1) ^ (row & 7)) << 4)) = hi;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive_cluster(lead(full_u(s)));
-        mbar_arrive(empty_p(sp));
-      }
-      return true;
-    };
-    for (int t = pair; ok && t < total_tiles; t += npairs) {
-      const int mt = t % p.tiles_m, nt = t / p.tiles_m;
-      for (int kb = 0; kb < p.kb_total && ok; ++kb, ++kbg) {
-        ok = widen(wq, kbg);
-        wq += has_tail ? 3 : 1;
-      }
-      if (!ok) break;
-      if (!(ok = mbar_wait(acc_full, pha, abort_flag, 0x40000u))) break;
-      tc_fence_after();
-      const int row = (2 * mt + (int)rank) * P_BM + quad * 32 + lane;
-      const bool row_ok = row < p.M;
-      const float sx = row_ok ? p.sx[row] : 0.0f;
-      const size_t rowoff = (size_t)row * p.N;
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t ri[32], rf[32];
-        __syncwarp();
-        tmem_ld32(lane_addr + (uint32_t)c0, ri);
-        if (has_tail) {
-          tmem_ld32(lane_addr + (uint32_t)(BN + c0), rf);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) rf[i] = 0u;
-        }
-        const int n0 = nt * BN + c0;
-        if (!row_ok || n0 >= p.N) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int n = n0 + 8 * j;
-          if (n < p.N) {
-            float d[8];
-            const float4 w0 = *reinterpret_cast<const float4*>(p.sw + n);
-            const float4 w1 = *reinterpret_cast<const float4*>(p.sw + n + 4);
-            const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float dense = __fmul_rn(__fmul_rn((float)((int)ri[8 * j + i] >> 4), sx), ws[i]);
-              d[i] = has_tail ? __fadd_rn(dense, __uint_as_float(rf[8 * j + i])) : dense;
-            }
-            if (p.bias) {
-              const float4 b0 = *reinterpret_cast<const float4*>(p.bias + n);
-              const float4 b1 = *reinterpret_cast<const float4*>(p.bias + n + 4);
-              const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-              for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], bs[i]);
-            }
-            uint4 o;
-            o.x = f32_to_bf16_bits(d[0]) | (f32_to_bf16_bits(d[1]) << 16);
-            o.y = f32_to_bf16_bits(d[2]) | (f32_to_bf16_bits(d[3]) << 16);
-            o.z = f32_to_bf16_bits(d[4]) | (f32_to_bf16_bits(d[5]) << 16);
-            o.w = f32_to_bf16_bits(d[6]) | (f32_to_bf16_bits(d[7]) << 16);
-            *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
-            if (p.dbg_acc) {
-              *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n) =
-                  make_int4((int)ri[8 * j] >> 4, (int)ri[8 * j + 1] >> 4, (int)ri[8 * j + 2] >> 4, (int)ri[8 * j + 3] >> 4);
-              *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n + 4) =
-                  make_int4((int)ri[8 * j + 4] >> 4, (int)ri[8 * j + 5] >> 4, (int)ri[8 * j + 6] >> 4, (int)ri[8 * j + 7] >> 4);
-            }
-            if (p.dbg_tail) {
-              *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n) = make_uint4(rf[8 * j], rf[8 * j + 1], rf[8 * j + 2], rf[8 * j + 3]);
-              *reinterpret_cast<uint4*>(p.dbg_tail + rowoff + n + 4) = make_uint4(rf[8 * j + 4], rf[8 * j + 5], rf[8 * j + 6], rf[8 * j + 7]);
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      mbar_arrive_cluster(lead(acc_empty));
-      pha ^= 1u;
+    const int step = has_tail ? 1 : 2;
+    for (int g = 0; g < G && ok; g += step) {
+      if (!(ok = widen_one(g, etid))) break;
+      const int i = g / kbt, kb = g - i * kbt;
+      if (kb >= look - 1 || kb + step >= kbt) catch_up(i);  // (second case: this group's last slice of the tile)
     }
+    catch_up(my_tiles);
   } else {
-    // ------------------------------------------------------------------ tail builders
+    // ------------------------------------------------------------------ tail builders (+ epilogue share)
     // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
     // bf16 tail tile of that half.  The row's entries of a slice come as one record column
     // ([slice][j][row]: a warp reads 128 contiguous bytes per j), fetched two slices ahead; the record
@@ -323,88 +373,107 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       const int brow = btid & 127, half = btid >> 7;
       const uint32_t roff = (uint32_t)((brow >> 3) * 1024 + (brow & 7) * 128);
       const uint32_t halfbit = (uint32_t)half << 6;
-      bool ok = true;
-      int q = 1 + half;
-      for (int t = pair; ok && t < total_tiles; t += npairs) {
-        const int mt = 2 * (t % p.tiles_m) + (int)rank;  // this CTA's 128-row tile
-        const int grow = mt * P_BM + brow;
-        const uint32_t* recb = p.rec + (size_t)mt * p.kb_total * C * 128 + brow;
-        const uint16_t* cntb = p.cnt + (size_t)mt * p.kb_total * 128 + brow;
-        auto fetch = [&](uint32_t(&r)[C], int& n, int kb) {
-          if (kb < p.kb_total) {
-            uint32_t n16;
-            asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 128));
-            n = (int)n16;
+      // records and count of K slice g (over all tiles of the pair)
+      auto fetch = [&](uint32_t(&r)[C], int& n, int g) {
+        if (g < G) {
+          const int i = g / kbt, kb = g - i * kbt;
+          const int mt = 2 * tile_mt(i) + (int)rank;  // this CTA's 128-row tile
+          const uint32_t* recb = p.rec + ((size_t)mt * kbt + kb) * C * 128 + brow;
+          uint32_t n16;
+          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + ((size_t)mt * kbt + kb) * 128 + brow));
+          n = (int)n16;
 #pragma unroll
-            for (int j = 0; j < C; ++j)
-              asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + ((size_t)kb * C + j) * 128));
-          } else {
-            n = 0;
-          }
-        };
-        auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {
-          const int s = slot_of(q);
-          if (!mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u)) return false;
-          tc_fence_after();
-          unsigned char* arow = sm + s * S::SLOT + roff;
-          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+          for (int j = 0; j < C; ++j) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + (size_t)j * 128));
+        } else {
+          n = 0;
+        }
+      };
+      auto fill = [&](int g, const uint32_t(&r)[C], int n) -> bool {
+        const int q = 3 * g + 1 + half, s = slot_of(q);
+        if (brow == 0) TQ_TRACE(4, q, 0);
+        if (!TQ_WAIT(9, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u))) return false;
+        if (brow == 0) TQ_TRACE(4, q, 1);
+        tc_fence_after();
+        unsigned char* arow = sm + s * S::SLOT + roff;
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
+        if (brow == 0) TQ_TRACE(5, q, 2);
 #pragma unroll
-          for (int j = 0; j < C; ++j) {
-            if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
-              *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
-          }
-          if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
-            const size_t lrow = (size_t)grow;
-            const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
-            const int lo = e0 + C, hi = e0 + n;  // list positions [lo, hi)
-            const int kb0 = kb * P_BK + 64 * half;
-            if ((p.ld & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.val)) & 15) == 0) {
-              const uint4* irow = reinterpret_cast<const uint4*>(p.idx + lrow * p.ld);
-              const uint4* vrow = reinterpret_cast<const uint4*>(p.val + lrow * p.ld);
-              for (int g8 = lo >> 3; g8 <= (hi - 1) >> 3; ++g8) {
-                const uint4 gi = __ldg(irow + g8), gv = __ldg(vrow + g8);
-                const uint32_t wi[4] = {gi.x, gi.y, gi.z, gi.w}, wv[4] = {gv.x, gv.y, gv.z, gv.w};
+        for (int j = 0; j < C; ++j) {
+          if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
+            *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
+        }
+        if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
+          const int i = g / kbt, kb = g - i * kbt;
+          const size_t lrow = (size_t)(2 * tile_mt(i) + (int)rank) * P_BM + brow;
+          const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+          const int lo = e0 + C, hi = e0 + n;  // list positions [lo, hi)
+          const int kb0 = kb * P_BK + 64 * half;
+          if ((p.ld & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.val)) & 15) == 0) {
+            const uint4* irow = reinterpret_cast<const uint4*>(p.idx + lrow * p.ld);
+            const uint4* vrow = reinterpret_cast<const uint4*>(p.val + lrow * p.ld);
+            for (int g8 = lo >> 3; g8 <= (hi - 1) >> 3; ++g8) {
+              const uint4 gi = __ldg(irow + g8), gv = __ldg(vrow + g8);
+              const uint32_t wi[4] = {gi.x, gi.y, gi.z, gi.w}, wv[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                  const int e = g8 * 8 + u;
-                  const int c = (int)((wi[u >> 1] >> ((u & 1) * 16)) & 0xffffu) - kb0;
-                  if (e >= lo && e < hi && c >= 0 && c < 64)
-                    *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
-                        (uint16_t)(wv[u >> 1] >> ((u & 1) * 16));
-                }
-              }
-            } else {
-              for (int e = lo; e < hi; ++e) {
-                const int c = (int)__ldg(p.idx + lrow * p.ld + e) - kb0;
-                if (c >= 0 && c < 64)
+              for (int u = 0; u < 8; ++u) {
+                const int e = g8 * 8 + u;
+                const int c = (int)((wi[u >> 1] >> ((u & 1) * 16)) & 0xffffu) - kb0;
+                if (e >= lo && e < hi && c >= 0 && c < 64)
                   *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
-                      __ldg(p.val + lrow * p.ld + e);
+                      (uint16_t)(wv[u >> 1] >> ((u & 1) * 16));
               }
             }
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(lead(full_u(s)));
-          q += 3;
-          return true;
-        };
-        uint32_t ra[C], rb[C];
-        int na = 0, nb = 0;
-        fetch(ra, na, 0);
-        fetch(rb, nb, 1);
-        for (int kb = 0; kb < p.kb_total && ok; kb += 2) {
-          ok = fill(kb, ra, na);
-          if (!ok) break;
-          fetch(ra, na, kb + 2);
-          if (kb + 1 < p.kb_total) {
-            ok = fill(kb + 1, rb, nb);
-            if (!ok) break;
-            fetch(rb, nb, kb + 3);
+          } else {
+            for (int e = lo; e < hi; ++e) {
+              const int c = (int)__ldg(p.idx + lrow * p.ld + e) - kb0;
+              if (c >= 0 && c < 64)
+                *reinterpret_cast<uint16_t*>(arow + (((c >> 3) ^ (brow & 7)) << 4) + (c & 7) * 2) =
+                    __ldg(p.val + lrow * p.ld + e);
+            }
           }
         }
+        if (brow == 0) TQ_TRACE(4, q, 3);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (brow == 0) TQ_TRACE(5, q, 0);
+        __syncwarp();
+        if (brow == 0) TQ_TRACE(5, q, 1);
+        if (lane == 0) mbar_arrive_cluster(lead(full_u(s)));
+        if (brow == 0) TQ_TRACE(4, q, 2);
+        return true;
+      };
+      // a tile's epilogue share comes after the first slices of the next tile, as for the wideners
+      auto after = [&](int g) -> bool {
+        const int i = g / kbt;
+        if (g - i * kbt >= look - 1) catch_up(i);
+        return ok;
+      };
+      uint32_t ra[C], rb[C];
+      int na = 0, nb = 0;
+      fetch(ra, na, 0);
+      fetch(rb, nb, 1);
+      for (int g = 0; g < G && ok; g += 2) {
+        ok = fill(g, ra, na) && after(g);
+        if (!ok) break;
+        fetch(ra, na, g + 2);
+        if (g + 1 < G) {
+          ok = fill(g + 1, rb, nb) && after(g + 1);
+          if (!ok) break;
+          fetch(rb, nb, g + 3);
+        }
       }
+      catch_up(my_tiles);
+    } else {
+      if (warp < 10) {  // warps 6..9: the odd K slices of the weight widening
+        const int wtid = threadIdx.x - 6 * 32;
+        for (int g = 1; g < G && ok; g += 2) {
+          if (!(ok = widen_one(g, wtid))) break;
+          const int i = g / kbt, kb = g - i * kbt;
+          if (kb >= look - 1 || kb + 2 >= kbt) catch_up(i);
+        }
+      }
+      catch_up(my_tiles);
     }
   }
 

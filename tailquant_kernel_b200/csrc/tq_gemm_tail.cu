@@ -52,6 +52,22 @@ __device__ unsigned long long g_wait_cycles[16];
 #define TQ_WAIT(slot, call) (call)
 #endif
 
+// Diagnostic build (-DTQ_GEMM_TRACE): clock64 stamps of CTA 0's roles for slot uses [TQ_TRACE_Q0, +128), in
+// g_trace[role][use][event]; read back with tq_gemm_trace().  Compiled out otherwise.
+#ifdef TQ_GEMM_TRACE
+#ifndef TQ_TRACE_Q0
+#define TQ_TRACE_Q0 30
+#endif
+__device__ unsigned long long g_trace[8][128][4];
+#define TQ_TRACE(role, q, ev)                                                              \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && (q) >= TQ_TRACE_Q0 && (q) < TQ_TRACE_Q0 + 128)                  \
+      g_trace[role][(q) - TQ_TRACE_Q0][ev] = (unsigned long long)clock64();                \
+  } while (0)
+#else
+#define TQ_TRACE(role, q, ev) do { } while (0)
+#endif
+
 constexpr int G_BM = 128;
 constexpr int G_BK = 128;
 constexpr int G_BUILD_WARPS = 8;
@@ -494,7 +510,7 @@ int launch_split_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_ro
 }  // namespace tq
 
 namespace tq {
-// -1 = default (one-CTA kernel), 0 = one-CTA kernel, 1 = CTA-pair kernel (initial value from TQ_GEMM_PAIR)
+// -1 = choose by shape, 0 = one-CTA kernel, 1 = CTA-pair kernel (initial value from TQ_GEMM_PAIR)
 static int g_gemm_pair_mode = [] {
   const char* e = getenv("TQ_GEMM_PAIR");
   return e ? atoi(e) : -1;
@@ -513,6 +529,18 @@ extern "C" int tq_gemm_wait_cycles(unsigned long long* out16, int reset) {
   if (reset) {
     unsigned long long z[16] = {};
     cudaMemcpyToSymbol(tq::g_wait_cycles, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
+#ifdef TQ_GEMM_TRACE
+extern "C" int tq_gemm_trace(unsigned long long* out, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, tq::g_trace, sizeof(unsigned long long) * 8 * 128 * 4);
+  if (reset) {
+    static unsigned long long z[8 * 128 * 4] = {};
+    cudaMemcpyToSymbol(tq::g_trace, z, sizeof(z));
   }
   return 0;
 }
@@ -543,9 +571,13 @@ extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, co
     return TQ_ERR_MISALIGNED;
   if (M == 0) return TQ_OK;
   {
-    // The CTA-pair kernel (256 x 256 tiles, half the B traffic per CTA) measured 8-25 % slower than the one-CTA
-    // kernel on every shape tried, so it runs only when asked for (TQ_GEMM_PAIR=1 or tq_set_gemm_pair_mode(1)).
-    if (g_gemm_pair_mode == 1)
+    // Choice between the one-CTA kernel (128 x 256 tiles) and the CTA-pair kernel (256 x 256 tiles, half the B
+    // traffic per CTA), from timings over M = 256..8192 on the Qwen3-8B and Llama-3-8B layer shapes: without a
+    // tail the pair kernel is 1.7-2x faster (two widening groups, epilogue shared by twelve warps); with a
+    // tail the two are within 5 % for K <= 8192 (pairs ahead up to M = 4096) and the one-CTA kernel is 20-30 %
+    // faster for the long-K projections.  TQ_GEMM_PAIR=0 / 1 or tq_set_gemm_pair_mode() force one of them.
+    const bool pair = g_gemm_pair_mode == 1 || (g_gemm_pair_mode < 0 && (R == 0 || (K < 8192 && M <= 4096)));
+    if (pair)
       return run_pair_gemm(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld,
                            tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, (cudaStream_t)stream);
   }

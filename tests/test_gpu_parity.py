@@ -331,7 +331,11 @@ def test_prologue_int8_operand(kind, K, M, R):
                                                   (300, 1032, 4096, 205, False, False),
                                                   (129, 136, 12288, 615, True, False),
                                                   (2048, 512, 256, 13, False, False), (1, 8, 128, 3, False, False),
-                                                  (140, 264, 1024, 205, False, True)])
+                                                  (140, 264, 1024, 205, False, True),
+                                                  # several tiles per CTA (pair) with one to three K slices each
+                                                  (2304, 4608, 128, 0, False, False),
+                                                  (2304, 4608, 256, 0, True, False),
+                                                  (2304, 4608, 384, 19, False, False)])
 @pytest.mark.parametrize("pair", [0, 1])
 def test_split_gemm_mma(M, N, K, R, bias, cluster, pair):
     """Fused kernel: int32 accumulators bit-exact, tensor-core tail within fp32 accumulation error of the
