@@ -4,11 +4,14 @@
 //   1. rotation in fp32 with ascending butterfly strides: radix-16 register passes, the row
 //      travelling between passes through a swizzled fp32 buffer in shared memory;
 //   2. one fp32 multiply by the normalisation and one rounding to bf16;
+//      -- the bf16 row is parked in shared memory and from here on a thread owns groups of 8
+//      consecutive indices (group tid + 256 j), so that packing and prefixes need no exchange;
 //   3. exact rank selection on the 15-bit magnitude keys (distance from the row maximum:
 //      128-wide coarse bins counted in registers, then a 128-bin shared histogram);
-//   4. tail membership with ties broken by lowest index (ballot bitmaps + a prefix over
-//      16-wide groups), tail entries emitted in ascending index order;
-//   5. INT4 codes of the body with true-division semantics, nibble pack, coalesced stores.
+//   4. tail membership with ties broken by lowest index (per-group masks + one block scan in
+//      index order), tail entries emitted in ascending index order;
+//   5. INT4 codes of the body with true-division semantics, packed / INT8 words stored straight
+//      to global memory (4 or 8 contiguous bytes per lane).
 //
 // Reference behaviour covered: tools/fused_threshold_topr_pack_ext_v57.py:96-194 (select,
 // scales, pack), tools/fused_topr_pack_ext_v55.py:21-26,73-109 (clamp_s4, scale = max(key,
@@ -230,20 +233,23 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
   static_assert(!BLOCK || K % 2048 == 0, "block-128 rotation needs K % 2048 == 0");
   static_assert(KIND != TQ_HAD_KRON12 || (L % 256 == 0), "kron12 needs K = 12 * 2^n, n >= 8");
 
+  constexpr int GN = K / 8;                  // groups of 8 consecutive indices
+  constexpr int J = (GN + NT - 1) / NT;      // groups per thread: g = tid + NT * j
+  constexpr int EJ = 8 * J;
+  constexpr int NSL = K / 128;               // 128-wide slices (K % 128 == 0 for every built K)
+  static_assert(J * (NT / 32) <= 64, "scan scratch");
+
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* buf = reinterpret_cast<float*>(smem_raw);
-  // aliases of buf, valid once the rotation has left it
-  uint8_t* pack_s = smem_raw;
-  uint16_t* bm_gt = reinterpret_cast<uint16_t*>(smem_raw + K / 2);
-  uint16_t* bm_eq = reinterpret_cast<uint16_t*>(smem_raw + K / 2 + K / 8);
-  uint32_t* prefix = reinterpret_cast<uint32_t*>(smem_raw + K / 2 + K / 4);
-  int8_t* q8_s = reinterpret_cast<int8_t*>(smem_raw + K);  // [K] INT8 codes in GEMM operand order
-  unsigned char* after = smem_raw + (size_t)K * 4;
-  uint32_t* hist = reinterpret_cast<uint32_t*>(after);
+  float* buf = reinterpret_cast<float*>(smem_raw);                           // [K] fp32, rotation passes
+  uint16_t* rowb = reinterpret_cast<uint16_t*>(smem_raw + (size_t)K * 4);    // [K] rotated row as bf16 bits
+  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw + (size_t)K * 6);
   uint32_t* red = hist + 128;
   int* res = reinterpret_cast<int*>(red + 32);
+  uint32_t* scan_a = reinterpret_cast<uint32_t*>(res + 8);  // [J][8] warp totals, then their exclusive scan
+  uint32_t* scan_b = scan_a + 64;
+  uint32_t* slice_pre = scan_b + 64;                         // [NSL] packed prefix at the start of each slice
   const int Rpad = (p.R + 7) & ~7;
-  uint16_t* st_idx = reinterpret_cast<uint16_t*>(res + 8);
+  uint16_t* st_idx = reinterpret_cast<uint16_t*>(slice_pre + ((NSL + 4) & ~3));
   uint16_t* st_val = st_idx + Rpad;
   int8_t* st_q = reinterpret_cast<int8_t*>(st_val + Rpad);
 
@@ -319,23 +325,39 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
       for (int g = 0; g < E / 8; ++g) butterflies<8>(v + g * 8);  // strides 16, 32, 64
     }
 
-    // ---- normalise, round to bf16, keys
-    uint32_t pk[E];
+    // ---- normalise, round to bf16; the row goes to shared memory in index order
     uint32_t kmax = 0;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      uint32_t b = f32_to_bf16_bits(v[e] * p.hscale);
-      pk[e] = b << 16;
+      const uint32_t b = f32_to_bf16_bits(v[e] * p.hscale);
+      rowb[fbase + eoff(e)] = (uint16_t)b;
       kmax = max(kmax, b & 0x7fffu);
     }
-    kmax = block_max(kmax, red, tid);  // also orders every read of buf before its reuse below
+    kmax = block_max(kmax, red, tid);  // its barriers also publish rowb and retire the last reads of buf
+
+    // ---- keys of this thread's groups: (bf16 bits << 16) | distance from the row maximum
+    uint32_t pk[EJ];
 #pragma unroll
-    for (int e = 0; e < E; ++e) pk[e] |= kmax - ((pk[e] >> 16) & 0x7fffu);
+    for (int j = 0; j < J; ++j) {
+      const int g = tid + NT * j;
+      const bool act = (GN % NT == 0) || g < GN;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      if (act) {
+        w = *reinterpret_cast<const uint4*>(rowb + 8 * g);
+        if (p.x_rot) *reinterpret_cast<uint4*>(p.x_rot + (size_t)m * K + 8 * g) = w;
+      }
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t b = (ww[c >> 1] >> (16 * (c & 1))) & 0xffffu;
+        pk[8 * j + c] = act ? ((b << 16) | (kmax - (b & 0x7fffu))) : 0xffffu;  // idle groups: beyond every bin
+      }
+    }
 
     // ---- rank selection
     int Tkp = -1, cnt_lt = 0, body_kp = 0;
     if (R > 0) {
-      SelRes s = select_rank<E>(pk, R, red, hist, res, tid);
+      SelRes s = select_rank<EJ>(pk, R, red, hist, res, tid);
       Tkp = s.kp;
       cnt_lt = s.cnt_lt;
       if (p.dr > s.cnt_lt && p.dr <= s.cnt_lt + s.cnt_eq) {
@@ -343,157 +365,148 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
       } else if (p.dr == s.cnt_lt + s.cnt_eq + 1 && s.next_kp >= 0) {
         body_kp = s.next_kp;
       } else {
-        body_kp = select_rank<E>(pk, p.dr, red, hist, res, tid).kp;
+        body_kp = select_rank<EJ>(pk, p.dr, red, hist, res, tid).kp;
       }
     } else if (p.dr > 1) {
-      body_kp = select_rank<E>(pk, p.dr, red, hist, res, tid).kp;
+      body_kp = select_rank<EJ>(pk, p.dr, red, hist, res, tid).kp;
     }
-    const int need = R - cnt_lt;
+    const int need = R - cnt_lt;  // keys equal to the threshold that still belong to the tail (lowest indices)
     const float tscale = make_scale(bf16_bits_to_f32(kmax), p.eps, p.scale_mode);
     const float bscale = make_scale(bf16_bits_to_f32(kmax - (uint32_t)body_kp), p.eps, p.scale_mode);
     const float brinv = __fdiv_rn(1.0f, bscale), trinv = __fdiv_rn(1.0f, tscale);
 
-    // ---- tail bitmaps (16 consecutive indices per half warp) and their prefix
+    // ---- tail membership: per-group masks, block scan of (larger | equal << 16) counts in index order
+    uint32_t mg[J], me[J], tm[J], pre[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) mg[j] = me[j] = tm[j] = pre[j] = 0u;
     if (R > 0) {
+      uint32_t cnt[J], incl[J];
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const int kp = (int)(pk[e] & 0xffffu);
-        unsigned bg = __ballot_sync(FULL, kp < Tkp), be = __ballot_sync(FULL, kp == Tkp);
-        if ((lane & 15) == 0) {
-          const int g = (fbase + eoff(e)) >> 4;
-          bm_gt[g] = (uint16_t)(bg >> (lane & 16));
-          bm_eq[g] = (uint16_t)(be >> (lane & 16));
+      for (int j = 0; j < J; ++j) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int kp = (int)(pk[8 * j + c] & 0xffffu);
+          mg[j] |= (uint32_t)(kp < Tkp) << c;
+          me[j] |= (uint32_t)(kp == Tkp) << c;
         }
+        cnt[j] = (uint32_t)__popc(mg[j]) | ((uint32_t)__popc(me[j]) << 16);
+        incl[j] = cnt[j];
       }
-      __syncthreads();
-      constexpr int G = K / 16, GPT = (G + NT - 1) / NT;
-      uint32_t loc[GPT], s = 0;
-#pragma unroll
-      for (int j = 0; j < GPT; ++j) {
-        const int g = tid * GPT + j;
-        loc[j] = (g < G) ? ((uint32_t)__popc(bm_gt[g]) | ((uint32_t)__popc(bm_eq[g]) << 16)) : 0u;
-        s += loc[j];
-      }
-      uint32_t incl = s;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        uint32_t t = __shfl_up_sync(FULL, incl, o);
-        if (lane >= o) incl += t;
-      }
-      if (lane == 31) red[warp] = incl;
-      __syncthreads();
-      uint32_t run = incl - s;
-      for (int w = 0; w < warp; ++w) run += red[w];
 #pragma unroll
-      for (int j = 0; j < GPT; ++j) {
-        const int g = tid * GPT + j;
-        if (g < G) prefix[g] = run;
-        run += loc[j];
-      }
-      __syncthreads();
-      if (p.tail_ptr) {  // run boundaries of the row's ascending index list at multiples of 128
-        for (int j = tid; j <= K / 128; j += NT) {
-          int cnt = R;
-          if (j < K / 128) {
-            const uint32_t pre = prefix[8 * j];
-            cnt = (int)(pre & 0xffffu) + min((int)(pre >> 16), R - cnt_lt);
-          }
-          p.tail_ptr[(size_t)m * p.ptr_ld + j] = (uint16_t)cnt;
+        for (int j = 0; j < J; ++j) {
+          const uint32_t t = __shfl_up_sync(FULL, incl[j], o);
+          if (lane >= o) incl[j] += t;
         }
       }
-      if (p.tail_cnt) {
-        for (int j = tid; j < K / 128; j += NT) {
-          const uint32_t pa = prefix[8 * j];
-          const int ea = (int)(pa & 0xffffu) + min((int)(pa >> 16), R - cnt_lt);
-          int eb = R;
-          if (j + 1 < K / 128) {
-            const uint32_t pb = prefix[8 * (j + 1)];
-            eb = (int)(pb & 0xffffu) + min((int)(pb >> 16), R - cnt_lt);
+      if (lane == 31) {
+#pragma unroll
+        for (int j = 0; j < J; ++j) scan_a[j * (NT / 32) + warp] = incl[j];
+      }
+      __syncthreads();
+      if (warp == 0) {  // exclusive scan of the J x 8 warp totals, two per lane
+        constexpr int NTOT = J * (NT / 32);
+        const uint32_t a0 = (2 * lane < NTOT) ? scan_a[2 * lane] : 0u;
+        const uint32_t a1 = (2 * lane + 1 < NTOT) ? scan_a[2 * lane + 1] : 0u;
+        uint32_t sc = a0 + a1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t t = __shfl_up_sync(FULL, sc, o);
+          if (lane >= o) sc += t;
+        }
+        const uint32_t ex = sc - (a0 + a1);
+        scan_b[2 * lane] = ex;
+        scan_b[2 * lane + 1] = ex + a0;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const int g = tid + NT * j;
+        pre[j] = scan_b[j * (NT / 32) + warp] + incl[j] - cnt[j];
+        if (((GN % NT == 0) || g < GN) && (g & 15) == 0) slice_pre[g >> 4] = pre[j];
+        tm[j] = mg[j];
+        if (me[j]) {  // ties at the threshold: the `need` lowest indices of the row join the tail
+          int neq = (int)(pre[j] >> 16);
+          uint32_t mm = me[j];
+          while (mm) {
+            const int c = __ffs(mm) - 1;
+            mm &= mm - 1u;
+            if (neq < need) tm[j] |= 1u << c;
+            ++neq;
           }
-          p.tail_cnt[((size_t)(m >> 7) * (K / 128) + j) * 128 + (m & 127)] = (uint16_t)(eb - ea);
+        }
+      }
+      __syncthreads();
+      // entries of the row's ascending list before a slice: the larger keys, plus the ties that made it
+      auto slice_start = [&](int sl) -> int {
+        const uint32_t ps = slice_pre[sl];
+        return (int)(ps & 0xffffu) + min((int)(ps >> 16), need);
+      };
+      if (p.tail_ptr) {  // run boundaries of the row's ascending index list at multiples of 128
+        for (int sl = tid; sl <= NSL; sl += NT)
+          p.tail_ptr[(size_t)m * p.ptr_ld + sl] = (uint16_t)(sl < NSL ? slice_start(sl) : R);
+      }
+      if (p.tail_cnt) {
+        for (int sl = tid; sl < NSL; sl += NT) {
+          const int ea = slice_start(sl), eb = sl + 1 < NSL ? slice_start(sl + 1) : R;
+          p.tail_cnt[((size_t)(m >> 7) * NSL + sl) * 128 + (m & 127)] = (uint16_t)(eb - ea);
+        }
+      }
+      // ---- tail entries, ascending index order
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const int g = tid + NT * j;
+        uint32_t mm = tm[j];
+        while (mm) {
+          const int c = __ffs(mm) - 1;
+          mm &= mm - 1u;
+          const uint32_t below = (1u << c) - 1u;
+          const int i = 8 * g + c;
+          const int pos = (int)(pre[j] & 0xffffu) + __popc(mg[j] & below) +
+                          min((int)(pre[j] >> 16) + __popc(me[j] & below), need);
+          const uint32_t vb = rowb[i];
+          st_idx[pos] = (uint16_t)i;
+          st_val[pos] = (uint16_t)vb;
+          if (p.tail_rec) {  // the entry's place in the record of its 128-wide slice
+            const int jr = pos - slice_start(i >> 7);
+            if (jr < TQ_TAIL_REC_CAP)
+              // bit 6: which 64-wide half; bits 0..5: half the byte offset of the value inside its
+              // 128-byte row of the swizzled operand tile (16-byte chunk index XOR row & 7, then the element)
+              p.tail_rec[(((size_t)(m >> 7) * NSL + (i >> 7)) * TQ_TAIL_REC_CAP + jr) * 128 + (m & 127)] =
+                  (uint32_t)(i & 64) | (uint32_t)(((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)) | (vb << 16);
+          }
+          if (p.top_q) st_q[pos] = (int8_t)quant_s4(bf16_bits_to_f32(vb), tscale, trinv);
         }
       }
     }
 
-    // ---- codes, tail entries
-    constexpr int NW = (E + 7) / 8;
-    uint32_t nw[NW];
+    // ---- INT4 codes of the body: 8 nibbles (packed form) and 8 bytes (INT8 form) per group, stored directly
 #pragma unroll
-    for (int i = 0; i < NW; ++i) nw[i] = 0;
+    for (int j = 0; j < J; ++j) {
+      const int g = tid + NT * j;
+      if ((GN % NT == 0) || g < GN) {
+        uint32_t packw = 0u, qlo = 0u, qhi = 0u;
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int kp = (int)(pk[e] & 0xffffu);
-      const uint32_t vb = pk[e] >> 16;
-      const float xv = bf16_bits_to_f32(vb);
-      bool is_tail = false;
-      if (R > 0) {
-        const bool gt = kp < Tkp, eq = kp == Tkp;
-        unsigned bg = __ballot_sync(FULL, gt), be = __ballot_sync(FULL, eq);
-        if (gt || eq) {
-          const int i = fbase + eoff(e);
-          const unsigned belowm = (1u << (lane & 15)) - 1u;
-          const unsigned mg = (bg >> (lane & 16)) & 0xffffu, me = (be >> (lane & 16)) & 0xffffu;
-          const uint32_t pre = prefix[i >> 4];
-          const int ngt = (int)(pre & 0xffffu) + __popc(mg & belowm);
-          const int neq = (int)(pre >> 16) + __popc(me & belowm);
-          is_tail = gt || (neq < need);
-          if (is_tail) {
-            const int pos = ngt + min(neq, need);
-            st_idx[pos] = (uint16_t)i;
-            st_val[pos] = (uint16_t)vb;
-            if (p.tail_rec) {  // the entry's place in the record of its 128-wide slice
-              const uint32_t ps = prefix[(i >> 7) << 3];
-              const int j = pos - ((int)(ps & 0xffffu) + min((int)(ps >> 16), need));
-              if (j < TQ_TAIL_REC_CAP)
-                // bit 6: which 64-wide half; bits 0..5: half the byte offset of the value inside its
-                // 128-byte row of the swizzled operand tile (16-byte chunk index XOR row & 7, then the element)
-                p.tail_rec[(((size_t)(m >> 7) * (K / 128) + (i >> 7)) * TQ_TAIL_REC_CAP + j) * 128 + (m & 127)] =
-                    (uint32_t)(i & 64) | (uint32_t)(((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)) | (vb << 16);
-            }
-            if (p.top_q) st_q[pos] = (int8_t)quant_s4(xv, tscale, trinv);
-          }
+        for (int c = 0; c < 8; ++c) {
+          const float xv = bf16_bits_to_f32(pk[8 * j + c] >> 16);
+          const int code = ((tm[j] >> c) & 1u) ? 0 : quant_s4(xv, bscale, brinv);
+          packw |= ((uint32_t)code & 0xfu) << (4 * c);
+          // INT8 form: even elements of the group first, then the odd ones -- the order in which the GEMM's
+          // widening of the packed INT4 weights lays out K
+          if (c & 1)
+            qhi |= ((uint32_t)code & 0xffu) << (8 * (c >> 1));
+          else
+            qlo |= ((uint32_t)code & 0xffu) << (8 * (c >> 1));
         }
-      }
-      const int code = is_tail ? 0 : quant_s4(xv, bscale, brinv);
-      nw[e >> 3] |= ((uint32_t)code & 0xfu) << (4 * (e & 7));
-      if (p.a_q8) {
-        // even elements of each 8-group first, then the odd ones: the order in which the GEMM's
-        // widening of the packed INT4 weights lays out K
-        const int i = fbase + eoff(e);
-        q8_s[(i & ~7) + ((i & 7) >> 1) + ((i & 1) << 2)] = (int8_t)code;
-      }
-      if (p.x_rot) p.x_rot[(size_t)m * K + fbase + eoff(e)] = (uint16_t)vb;
-    }
-    // nibbles of index pairs (2i, 2i+1) sit in adjacent lanes: exchange and form bytes
-    {
-      const int fb_even = BLOCK ? (((tid & ~1) & 15) + 128 * (tid >> 4)) : (tid & ~1);
-#pragma unroll
-      for (int i = 0; i < NW; ++i) {
-        const uint32_t other = __shfl_xor_sync(FULL, nw[i], 1);
-        const uint32_t we = (lane & 1) ? other : nw[i], wo = (lane & 1) ? nw[i] : other;
-        const uint32_t bytes = (lane & 1) ? (((we >> 4) & 0x0f0f0f0fu) | (wo & 0xf0f0f0f0u))
-                                          : ((we & 0x0f0f0f0fu) | ((wo & 0x0f0f0f0fu) << 4));
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int e = 8 * i + 2 * b + (lane & 1);
-          if (e < E) pack_s[(fb_even + eoff(e)) >> 1] = (uint8_t)(bytes >> (8 * b));
-        }
+        if (p.a_pack) *reinterpret_cast<uint32_t*>(p.a_pack + (size_t)m * (K / 2) + 4 * g) = packw;
+        if (p.a_q8) *reinterpret_cast<uint2*>(p.a_q8 + (size_t)m * K + 8 * g) = make_uint2(qlo, qhi);
       }
     }
     __syncthreads();
 
-    // ---- coalesced copy-out
+    // ---- coalesced copy-out of the tail lists
     {
-      if (p.a_pack) {
-        uint4* dst = reinterpret_cast<uint4*>(p.a_pack + (size_t)m * (K / 2));
-        const uint4* src = reinterpret_cast<const uint4*>(pack_s);
-        for (int i = tid; i < K / 32; i += NT) dst[i] = src[i];
-      }
-      if (p.a_q8) {
-        uint4* dst = reinterpret_cast<uint4*>(p.a_q8 + (size_t)m * K);
-        const uint4* src = reinterpret_cast<const uint4*>(q8_s);
-        for (int i = tid; i < K / 16; i += NT) dst[i] = src[i];
-      }
       const size_t rb = (size_t)m * R, rl = (size_t)m * p.tail_ld;
       for (int r = tid; r < R; r += NT) {
         const uint16_t ix = st_idx[r];
@@ -507,7 +520,7 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
         if (p.top_scale) p.top_scale[m] = tscale;
       }
     }
-    __syncthreads();  // pack_s / bitmaps alias the rotation buffer of the next row
+    __syncthreads();  // the tail staging and the bf16 row are rewritten by the next row
   }
 }
 
@@ -515,7 +528,7 @@ template <int KIND, int K>
 int launch(const PrologueParams& p, cudaStream_t st) {
   auto kern = prologue_kernel<KIND, K>;
   const int Rpad = (p.R + 7) & ~7;
-  const size_t smem = (size_t)K * 4 + (128 + 32 + 8) * 4 + (size_t)Rpad * 5 + 16;
+  const size_t smem = (size_t)K * 6 + (128 + 32 + 8 + 64 + 64 + ((K / 128 + 4) & ~3)) * 4 + (size_t)Rpad * 5 + 16;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -581,7 +594,8 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
   if ((tail_rec != nullptr) != (tail_cnt != nullptr) || (tail_rec && K % 128 != 0)) return TQ_ERR_BAD_ARG;
   if (!x || (!a_pack && !a_q8) || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
   if (dr < 1 || dr > K) return TQ_ERR_BAD_ARG;
-  if (!aligned16(x) || (a_pack && !aligned16(a_pack)) || (a_q8 && !aligned16(a_q8))) return TQ_ERR_MISALIGNED;
+  if (!aligned16(x) || (a_pack && !aligned16(a_pack)) || (a_q8 && !aligned16(a_q8)) || (x_rot && !aligned16(x_rot)))
+    return TQ_ERR_MISALIGNED;
   if (M == 0) return TQ_OK;
   PrologueParams p;
   p.x = reinterpret_cast<const __nv_bfloat16*>(x);
