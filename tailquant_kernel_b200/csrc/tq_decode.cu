@@ -6,7 +6,8 @@
 //    staged once in shared memory.  Both operands are widened with the same nibble order (value x 16 in the
 //    top nibble, exact >> 8 afterwards) and multiplied with mma.sync m16n8k32 s8: with at most 64 rows the
 //    tensor-core rate is irrelevant, the weight stream is what takes time.  Partial sums are added with int32
-//    atomics into C, which the entry point zeroes first (integer addition: any order gives the same bits).
+//    atomics into C, which the entry point zeroes first (integer addition: any order gives the same bits); with a
+//    single K range the results are stored directly.
 //  * tail_small_kernel: the tail correction for few rows reads only the weight rows it needs (M*R rows of the
 //    [K,N] bf16 matrix) instead of streaming whole strips.  The sum over the R entries is split into eight
 //    interleaved fp32 fma chains (entry r goes to chain r mod 8) that are combined pairwise in a fixed order,
@@ -42,85 +43,118 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// MT = number of 16-row tiles of the activations (M <= 16 * MT).  A8: the activations arrive as INT8 codes in
-// the operand order of the prologue's a_q8 output (which is the byte order widen16 produces), so their
-// fragments are plain loads; otherwise they arrive packed and are widened like the weights.
-template <int MT, bool A8>
+// MT = number of 16-row tiles of the activations (M <= 16 * MT).  A8: shared memory holds the activations as
+// bytes in the order widen16 produces, so their fragments are plain loads.  SRC8: they also arrive that way, as
+// true INT8 codes -- the prologue's a_q8 output; otherwise they arrive packed and are widened (value x 16) either
+// while staging (A8; measured slower than per-fragment widening, kept as an instantiation option) or per fragment.
+template <int MT, bool A8, bool SRC8>
 __global__ void __launch_bounds__(DV_THREADS)
 gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b_col, int32_t* __restrict__ C, int M,
-               int N, int K, int k_per_split) {
+               int N, int K, int k_per_split, int direct, int cgroups) {
   extern __shared__ __align__(16) unsigned char sm_a[];  // [16*MT rows][pitch] packed activations of this K range
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
   const int k0 = blockIdx.y * k_per_split;
   const int k1 = min(K, k0 + k_per_split);
   if (k0 >= k1) return;
-  constexpr int AB = A8 ? 1 : 2;           // K elements per activation byte
-  const int kbytes = (k1 - k0) / AB;       // activation bytes per row in this range
-  const int pitch = kbytes + 64;           // consecutive rows start 64 bytes apart modulo 128: no bank conflicts
-
-  for (int i = tid; i < 16 * MT * (kbytes / 16); i += DV_THREADS) {
-    const int row = i / (kbytes / 16), piece = i % (kbytes / 16);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < M) v = *reinterpret_cast<const uint4*>(a_pack + (size_t)row * (K / AB) + k0 / AB + piece * 16);
-    *reinterpret_cast<uint4*>(sm_a + row * pitch + piece * 16) = v;
-  }
-  __syncthreads();
-
-  const int n = blockIdx.x * DV_CH + warp * 8 + g;  // channel whose weights this lane streams
-  const uint8_t* wrow = b_col + (size_t)min(n, N - 1) * (K / 2) + k0 / 2 + j * 16;
-  int acc[MT][4];
-#pragma unroll
-  for (int t = 0; t < MT; ++t)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+  static_assert(A8 || !SRC8, "INT8 input is staged as bytes");
+  constexpr int AB = A8 ? 1 : 2;           // K elements per staged activation byte
+  constexpr int SB = SRC8 ? 1 : 2;         // K elements per input byte
+  const int kbytes = (k1 - k0) / AB;       // staged bytes per row in this range
+  // row pitch chosen so that the fragment loads of a quarter warp fall into distinct 16-byte bank groups
+  const int pitch = kbytes + (A8 ? 16 : 64);
 
   const int nslices = (k1 - k0) / DV_KS;
-  constexpr int PF = 4;  // weight loads kept in flight per lane
-  uint4 wq[PF];
+  constexpr int PF = MT <= 2 ? 8 : 4;  // weight loads kept in flight per lane
+  const bool hi_rows = M > 8;  // rows 8..15 of the (only) tile exist
+
+  // A CTA goes through `cgroups` groups of 64 channels with the same staged activations.
+  for (int cg = 0; cg < cgroups; ++cg) {
+    const int nbase = (blockIdx.x * cgroups + cg) * DV_CH;
+    if (nbase >= N) break;
+    // the weight stream starts first: it does not depend on the activations
+    const int n = nbase + warp * 8 + g;  // channel whose weights this lane streams
+    const uint8_t* wrow = b_col + (size_t)min(n, N - 1) * (K / 2) + k0 / 2 + j * 16;
+    uint4 wq[PF];
 #pragma unroll
-  for (int s = 0; s < PF; ++s)
-    wq[s] = (s < nslices && n < N) ? ldg_nc_128(wrow + (size_t)s * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
-  for (int s0 = 0; s0 < nslices; s0 += PF) {
+    for (int s = 0; s < PF; ++s)
+      wq[s] = (s < nslices && n < N) ? ldg_nc_128(wrow + (size_t)s * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+
+    if (cg == 0) {
+      const int in_bytes = (k1 - k0) / SB;  // input bytes per row in this range
+      for (int i = tid; i < 16 * MT * (in_bytes / 16); i += DV_THREADS) {
+        const int row = i / (in_bytes / 16), piece = i % (in_bytes / 16);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < M) v = *reinterpret_cast<const uint4*>(a_pack + (size_t)row * (K / SB) + k0 / SB + piece * 16);
+        if (A8 && !SRC8) {
+          uint32_t o[8];
+          widen16(v, o);
+          *reinterpret_cast<uint4*>(sm_a + row * pitch + piece * 32) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(sm_a + row * pitch + piece * 32 + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+        } else {
+          *reinterpret_cast<uint4*>(sm_a + row * pitch + piece * 16) = v;
+        }
+      }
+      __syncthreads();
+    }
+
+    int acc[MT][4];
 #pragma unroll
-    for (int u = 0; u < PF; ++u) {
-      const int s = s0 + u;
-      if (s < nslices) {
-        uint32_t b[8];
-        widen16(wq[u], b);
-        const int sn = s + PF;
-        wq[u] = (sn < nslices && n < N) ? ldg_nc_128(wrow + (size_t)sn * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+    for (int t = 0; t < MT; ++t)
 #pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          uint32_t a[8], c[8];
-          if (A8) {
-            const unsigned char* plo = sm_a + (16 * t + g) * pitch + s * DV_KS + j * 32;
-            const unsigned char* phi = sm_a + (16 * t + g + 8) * pitch + s * DV_KS + j * 32;
-            const uint4 l0 = *reinterpret_cast<const uint4*>(plo), l1 = *reinterpret_cast<const uint4*>(plo + 16);
-            const uint4 h0 = *reinterpret_cast<const uint4*>(phi), h1 = *reinterpret_cast<const uint4*>(phi + 16);
-            a[0] = l0.x, a[1] = l0.y, a[2] = l0.z, a[3] = l0.w, a[4] = l1.x, a[5] = l1.y, a[6] = l1.z, a[7] = l1.w;
-            c[0] = h0.x, c[1] = h0.y, c[2] = h0.z, c[3] = h0.w, c[4] = h1.x, c[5] = h1.y, c[6] = h1.z, c[7] = h1.w;
-          } else {
-            const uint4 alo = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g) * pitch + s * (DV_KS / 2) + j * 16);
-            const uint4 ahi = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g + 8) * pitch + s * (DV_KS / 2) + j * 16);
-            widen16(alo, a);
-            widen16(ahi, c);
+      for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+    for (int s0 = 0; s0 < nslices; s0 += PF) {
+#pragma unroll
+      for (int u = 0; u < PF; ++u) {
+        const int s = s0 + u;
+        if (s < nslices) {
+          uint32_t b[8];
+          widen16(wq[u], b);
+          const int sn = s + PF;
+          wq[u] = (sn < nslices && n < N) ? ldg_nc_128(wrow + (size_t)sn * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            uint32_t a[8], c[8];
+            if (A8) {
+              const unsigned char* plo = sm_a + (16 * t + g) * pitch + s * DV_KS + j * 32;
+              const unsigned char* phi = sm_a + (16 * t + g + 8) * pitch + s * DV_KS + j * 32;
+              const uint4 l0 = *reinterpret_cast<const uint4*>(plo), l1 = *reinterpret_cast<const uint4*>(plo + 16);
+              const uint4 h0 = *reinterpret_cast<const uint4*>(phi), h1 = *reinterpret_cast<const uint4*>(phi + 16);
+              a[0] = l0.x, a[1] = l0.y, a[2] = l0.z, a[3] = l0.w, a[4] = l1.x, a[5] = l1.y, a[6] = l1.z, a[7] = l1.w;
+              c[0] = h0.x, c[1] = h0.y, c[2] = h0.z, c[3] = h0.w, c[4] = h1.x, c[5] = h1.y, c[6] = h1.z, c[7] = h1.w;
+            } else {
+              const uint4 alo = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g) * pitch + s * (DV_KS / 2) + j * 16);
+              widen16(alo, a);
+              if (MT > 1 || hi_rows) {
+                const uint4 ahi = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g + 8) * pitch + s * (DV_KS / 2) + j * 16);
+                widen16(ahi, c);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) c[i] = 0u;
+              }
+            }
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) mma_s8(acc[t], a[2 * qd], c[2 * qd], a[2 * qd + 1], c[2 * qd + 1], b[2 * qd], b[2 * qd + 1]);
           }
-#pragma unroll
-          for (int qd = 0; qd < 4; ++qd) mma_s8(acc[t], a[2 * qd], c[2 * qd], a[2 * qd + 1], c[2 * qd + 1], b[2 * qd], b[2 * qd + 1]);
         }
       }
     }
-  }
 
-  // accumulator fragment: rows g and g + 8 of the tile, channels 2j and 2j + 1 of the warp's eight
-  const int nc = blockIdx.x * DV_CH + warp * 8 + 2 * j;
+    // accumulator fragment: rows g and g + 8 of the tile, channels 2j and 2j + 1 of the warp's eight
+    const int nc = nbase + warp * 8 + 2 * j;
 #pragma unroll
-  for (int t = 0; t < MT; ++t) {
+    for (int t = 0; t < MT; ++t) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = 16 * t + g + ((i >> 1) << 3), col = nc + (i & 1);
-      if (row < M && col < N) atomicAdd(C + (size_t)row * N + col, acc[t][i] >> (A8 ? 4 : 8));
+      for (int i = 0; i < 4; ++i) {
+        const int row = 16 * t + g + ((i >> 1) << 3), col = nc + (i & 1);
+        if (row < M && col < N) {
+          const int v = acc[t][i] >> (SRC8 ? 4 : 8);  // one or both operands carry a factor 16
+          if (direct)
+            C[(size_t)row * N + col] = v;  // the only K range: no accumulation across CTAs
+          else
+            atomicAdd(C + (size_t)row * N + col, v);
+        }
+      }
     }
   }
 }
@@ -187,11 +221,11 @@ tail_small_kernel(const uint16_t* __restrict__ idx, const uint16_t* __restrict__
   }
 }
 
-template <int MT, bool A8>
+template <int MT, bool A8, bool SRC8>
 int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, int N, int K, int kps, int splits,
-                cudaStream_t st) {
-  const size_t smem = (size_t)16 * MT * (kps / (A8 ? 1 : 2) + 64);
-  auto kern = gemv_s4_kernel<MT, A8>;
+                int cgroups, cudaStream_t st) {
+  const size_t smem = (size_t)16 * MT * (A8 ? kps + 16 : kps / 2 + 64);
+  auto kern = gemv_s4_kernel<MT, A8, SRC8>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -203,8 +237,15 @@ int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, 
     }
     if (dev < 64) configured[dev] = true;
   }
-  dim3 grid((N + DV_CH - 1) / DV_CH, splits);
-  kern<<<grid, DV_THREADS, smem, st>>>(a_pack, b_col, C, M, N, K, kps);
+  dim3 grid((N + DV_CH * cgroups - 1) / (DV_CH * cgroups), splits);
+  if (splits > 1) {  // partial sums of the K ranges meet in C through atomics
+    cudaError_t e = cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), st);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return TQ_ERR_CUDA;
+    }
+  }
+  kern<<<grid, DV_THREADS, smem, st>>>(a_pack, b_col, C, M, N, K, kps, splits == 1 ? 1 : 0, cgroups);
   return check_launch();
 }
 
@@ -222,32 +263,32 @@ extern "C" int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, co
   if (M == 0) return TQ_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int slices = K / DV_KS;
-  if (split_k < 1) {  // enough CTAs for a few per SM, at least two K slices each
-    const int ctas_n = (N + DV_CH - 1) / DV_CH;
-    split_k = (4 * 148 + ctas_n - 1) / ctas_n;
+  const int mt = (M + 15) / 16;
+  // groups of 64 channels per CTA (sharing the staged activations): more than one measured slower at every M
+  // on the Qwen3-8B layer shapes -- the smaller grid costs more than the repeated staging
+  const int cgroups = 1;
+  if (split_k < 1) {  // four CTAs per SM, eight for the wide projections (timed on the Qwen3-8B layer shapes)
+    const int ctas_n = (N + DV_CH * cgroups - 1) / (DV_CH * cgroups);
+    split_k = ((ctas_n >= 256 ? 8 : 4) * 148 + ctas_n - 1) / ctas_n;
   }
   if (split_k > slices) split_k = slices;
   int sps = (slices + split_k - 1) / split_k;                 // slices per split
-  const int max_sps = (180 * 1024 / (16 * ((M + 15) / 16)) - 64) / (a8 ? DV_KS : DV_KS / 2);  // activation rows must fit in shared memory
+  const bool bytes_staged = a8;
+  // staged activation rows: at most 56 KB, four CTAs per SM
+  const int max_sps = (56 * 1024 / (16 * mt) - 64) / (bytes_staged ? DV_KS : DV_KS / 2);
   if (sps > max_sps) sps = max_sps;
   const int splits = (slices + sps - 1) / sps;
-  cudaError_t e = cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), st);
-  if (e != cudaSuccess) {
-    set_last_cuda_error(e);
-    return TQ_ERR_CUDA;
-  }
   const int kps = sps * DV_KS;
-  const int mt = (M + 15) / 16;
   if (a8) {
-    if (mt == 1) return launch_gemv<1, true>(a, b_col, C, M, N, K, kps, splits, st);
-    if (mt == 2) return launch_gemv<2, true>(a, b_col, C, M, N, K, kps, splits, st);
-    if (mt == 3) return launch_gemv<3, true>(a, b_col, C, M, N, K, kps, splits, st);
-    return launch_gemv<4, true>(a, b_col, C, M, N, K, kps, splits, st);
+    if (mt == 1) return launch_gemv<1, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+    if (mt == 2) return launch_gemv<2, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+    if (mt == 3) return launch_gemv<3, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+    return launch_gemv<4, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
   }
-  if (mt == 1) return launch_gemv<1, false>(a, b_col, C, M, N, K, kps, splits, st);
-  if (mt == 2) return launch_gemv<2, false>(a, b_col, C, M, N, K, kps, splits, st);
-  if (mt == 3) return launch_gemv<3, false>(a, b_col, C, M, N, K, kps, splits, st);
-  return launch_gemv<4, false>(a, b_col, C, M, N, K, kps, splits, st);
+  if (mt == 1) return launch_gemv<1, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+  if (mt == 2) return launch_gemv<2, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+  if (mt == 3) return launch_gemv<3, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+  return launch_gemv<4, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
 }
 
 extern "C" int tq_tail_gather_small(const uint16_t* tail_idx16, const void* tail_val, const void* w_t, float* tail,

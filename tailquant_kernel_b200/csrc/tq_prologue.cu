@@ -221,7 +221,7 @@ __device__ __forceinline__ float make_scale(float t, float eps, int mode) {
 }
 
 // resident CTAs per SM the register budget is tuned for
-constexpr int min_ctas(int K) { return K <= 4096 ? 3 : 2; }
+constexpr int min_ctas(int K) { return K <= 4096 ? 4 : 2; }
 
 template <int KIND, int K>
 __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const PrologueParams p) {
