@@ -221,10 +221,13 @@ def run_ours(args) -> None:
     dev_y = [torch.empty((M_TOKENS, lin.N), dtype=torch.bfloat16, device=dev) for lin in lins]
 
     def step_e2e():
+        # Steps are pipelined the way a serving loop would run them: the copy-in of step n + 1 starts as soon as
+        # linear i of step n has consumed its input buffer, and the copy-out of step n drains while step n + 1
+        # computes.  Every step still moves all of its inputs host -> device and all of its outputs device -> host.
         cur = torch.cuda.current_stream()
-        s_in.wait_stream(cur)
         with torch.cuda.stream(s_in):
             for i, (hx, dx) in enumerate(zip(host_x, dev_x)):
+                s_in.wait_event(ev_done[i])  # the previous step's linear i has read dx
                 dx.copy_(hx, non_blocking=True)
                 ev_in[i].record(s_in)
         for i, (lin, dx) in enumerate(zip(lins, dev_x)):
@@ -237,11 +240,17 @@ def run_ours(args) -> None:
                 s_out.wait_event(ev_done[i])
                 hy.copy_(dev_y[i], non_blocking=True)
                 ev_free[i].record(s_out)
+
+    def drain_e2e():
+        cur = torch.cuda.current_stream()
+        cur.wait_stream(s_in)
         cur.wait_stream(s_out)
 
-    def timed(fn, steps, warmup, sample_clocks=False):
+    def timed(fn, steps, warmup, sample_clocks=False, drain=None):
         for _ in range(warmup):
             fn()
+        if drain:
+            drain()
         barrier()
         sampler = ClockSampler(local) if sample_clocks else None
         if sampler:
@@ -250,6 +259,8 @@ def run_ours(args) -> None:
         e0.record()
         for _ in range(steps):
             fn()
+        if drain:
+            drain()  # the stop event waits for the copy streams: the last step's outputs are in host memory
         e1.record()
         torch.cuda.synchronize()
         clocks = sampler.stop() if sampler else None
@@ -262,7 +273,7 @@ def run_ours(args) -> None:
         return ms / steps, clocks
 
     ms_step, clocks = timed(step, args.steps, args.warmup, sample_clocks=True)
-    ms_e2e, _ = timed(step_e2e, args.steps, max(args.warmup, 3))
+    ms_e2e, _ = timed(step_e2e, args.steps, max(args.warmup, 3), drain=drain_e2e)
     assert ops.gemm_status() == 0, "a bounded device-side wait ran out during the benchmark"
 
     # ---- per-kernel device time over the same four linears (CUDA events on the launching stream)
@@ -322,6 +333,43 @@ def run_ours(args) -> None:
         b8 = torch.randint(-8, 8, (N, K), dtype=torch.int8, device=dev).t()
         int8_ms += kernel_ms(lambda: torch._int_mm(a8, b8))
         del a8, b8
+
+    # Layer latency the way the reference times its layers (CUDA graph, warm-ups, >= 30 replays; median of 5 runs):
+    # tools/bench_hadamard_three_schemes_quarot_dense_sharedqkv_inplace_fusedtopr_v43.py:105-123
+    def graph_median_ms(fn, replays=30, runs=5):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(5):
+            graph.replay()
+        torch.cuda.synchronize()
+        out = []
+        for _ in range(runs):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(replays):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            out.append(e0.elapsed_time(e1) / replays)
+        return sorted(out)[len(out) // 2]
+
+    Wbs = [torch.randn((N, K), device=dev, dtype=torch.bfloat16) * 0.02 for (_, K, N) in LAYER]
+
+    def step_bf16():
+        for x, Wb in zip(xs, Wbs):
+            torch.nn.functional.linear(x, Wb)
+
+    graph_split_ms = graph_median_ms(step)
+    graph_bf16_ms = graph_median_ms(step_bf16)
+    del Wbs
 
     peaks = load_peaks()
     ops_step = layer_ops(M_TOKENS)
@@ -392,6 +440,9 @@ def run_ours(args) -> None:
         "bf16_cublas_linear_ms_per_step": bf16_ms,
         "int8_cublas_gemm_ms_per_step": int8_ms,
         "split_over_bf16": ms_step / bf16_ms,
+        "graph_latency": {"split_layer_ms": graph_split_ms, "bf16_cublas_layer_ms": graph_bf16_ms,
+                          "split_over_bf16": graph_split_ms / graph_bf16_ms,
+                          "protocol": "one CUDA graph per layer (4 linears), 5 warm-ups, 30 replays, median of 5 runs"},
     }
     if not mma:
         line["kernels"]["tail_gather"] = {"ms_per_step": t_tail, "share": t_tail / t_sum,
@@ -420,7 +471,10 @@ def run_extra(args) -> None:
     """Secondary workloads of the baseline (one JSON line per case, device time by CUDA events):
     decode      : Qwen3-8B layer shapes at M in {1, 8, 32, 64}, split-K path, int4-weight GB/s against HBM peak
     llama_sweep : Llama-3-8B layer shapes at M = 4096, ratios 0 / 0.01 / 0.05 / 0.10 (K = 14336 uses block-128)
-    single      : baseline config 1 (M = 512, K = N = 4096, ratio 0.05), both tail engines"""
+    single      : baseline config 1 (M = 512, K = N = 4096, ratio 0.05), both tail engines
+    latency_table : CSV `K,N,ratio,b16,b64,b256` (ms per forward at 16 / 64 / 256 token rows, CUDA-graph replay) in
+                  the format the reference's policy calibrator reads
+                  (tools/calibrate_shape_latency_cegrad_ratio_v1.py:365-440), Qwen3-8B per-projection shapes"""
     import torch
     from tailquant_kernel_b200 import SplitLinear
 
@@ -468,21 +522,45 @@ def run_extra(args) -> None:
         for name, K, N in LAYER:
             _, W = data(1, K, N, 7)
             lin = SplitLinear(W, ratio=RATIO, tail_engine="gather")
+            n_copies = max(2, int((300 * 2 ** 20) // (K * N // 2)) + 1)
+            b_copies = [lin.w.b_col] + [lin.w.b_col.clone() for _ in range(n_copies - 1)]
             for M in (1, 8, 32, 64):
                 x, _ = data(M, K, N, 11 + M)
                 ws = lin.prologue(x)
                 from tailquant_kernel_b200 import ops as _ops
                 t_all = graph_ms_of(lambda: lin.forward(x))
-                t_gemm = graph_ms_of(lambda: _ops.gemv_splitk(ws.pro.a_pack, lin.w.b_col, ws.acc, 0))
+                # the weight stream is timed with the packed weights rotating through > 300 MB of copies inside
+                # one graph, so that every launch reads them from HBM and not from the 126 MB L2
+                def all_copies():
+                    for b in b_copies:
+                        _ops.gemv_splitk(ws.pro.a_pack, b, ws.acc, 0)
+                t_gemm = graph_ms_of(all_copies) / len(b_copies)
                 t_pro = graph_ms_of(lambda: lin.prologue(x))
                 t_tail = graph_ms_of(lambda: _ops.tail_gather_small(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R))
                 wbytes = K * N / 2
                 print(json.dumps({"workload": "decode", "linear": name, "M": M, "K": K, "N": N, "R": lin.R,
                                   "linear_ms": t_all, "splitk_gemm_ms": t_gemm,
-                                  "prologue_ms": t_pro, "tail_gather_ms": t_tail, "timing": "CUDA graph replay",
+                                  "prologue_ms": t_pro, "tail_gather_ms": t_tail,
+                                  "timing": "CUDA graph replay; splitk_gemm_ms = mean launch over %d weight copies "
+                                            "(HBM-resident), the other figures with L2-warm operands" % len(b_copies),
                                   "int4_weight_gbs": wbytes / (t_gemm * 1e-3) / 1e9,
                                   "frac_of_hbm_peak": wbytes / (t_gemm * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                   "tail_row_bytes": 2.0 * M * lin.R * N}), flush=True)
+            del b_copies
+    elif args.workload == "latency_table":
+        # the seven per-projection shapes of a Qwen3-8B layer (the policy's units), ratios of the policy grid
+        shapes = [(4096, 4096), (4096, 1024), (4096, 12288), (12288, 4096)]
+        print("K,N,ratio,b16,b64,b256", flush=True)
+        for K, N in shapes:
+            _, W = data(1, K, N, 21)
+            for ratio in (0.0, 0.01, 0.02, 0.05, 0.10, 0.16):
+                lin = SplitLinear(W, ratio=ratio)
+                cols = []
+                for M in (16, 64, 256):
+                    x, _ = data(M, K, N, 31 + M)
+                    cols.append(graph_ms_of(lambda: lin.forward(x)))
+                print(f"{K},{N},{ratio},{cols[0]:.5f},{cols[1]:.5f},{cols[2]:.5f}", flush=True)
+                del lin
     elif args.workload == "llama_sweep":
         shapes = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
         M = 4096
@@ -508,17 +586,22 @@ def run_extra(args) -> None:
 
 
 def main() -> None:
+    global M_TOKENS, METRIC
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--rows-per-gpu", type=int, default=M_TOKENS,
+                    help="token rows per GPU (2048 = the headline config; 4096 per GPU on 8 GPUs is the M = 32768 run)")
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tail-engine", default="mma", choices=["mma", "gather"],
                     help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
-    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single", "latency_table"],
                     help="layer = the benchmark proper (baseline configs[1]); the others print secondary figures")
     args = ap.parse_args()
+    M_TOKENS = args.rows_per_gpu
+    METRIC = METRIC.replace("M=2048/GPU", f"M={M_TOKENS}/GPU")
     if args.workload != "layer":
         run_extra(args)
         return

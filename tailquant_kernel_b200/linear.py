@@ -62,7 +62,55 @@ class SplitLinear:
                                     bias=bias)
         self.small_m = int(small_m)
         self.split_k = int(split_k)
+        self.activation_percentile = float(activation_percentile)
         self._ws: Dict[int, _Workspace] = {}
+
+    @classmethod
+    def from_prepared(cls, w: "ops.PreparedWeight", ratio: float = 0.05, activation_percentile: float = 100.0,
+                      small_m: int = 64, split_k: int = 0, tail_engine: str = "mma") -> "SplitLinear":
+        """A layer around weights that are already rotated and quantised (e.g. read by `SplitLinear.load`)."""
+        if tail_engine not in ("mma", "gather"):
+            raise RuntimeError("tail_engine must be 'mma' or 'gather'")
+        if not w.b_col.is_cuda:
+            raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
+        self = cls.__new__(cls)
+        self.tail_engine = tail_engine
+        self.N, self.K = int(w.N), int(w.K)
+        self.ratio = float(ratio)
+        self.R = ops.ceil_ratio_count(self.K, self.ratio)
+        _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
+        if self.R > 0 and tail_engine == "mma" and w.w_rot is None:
+            raise RuntimeError("the tensor-core tail needs the rotated bf16 weights (w_rot)")
+        if self.R > 0 and w.w_t is None and w.w_rot is not None:
+            # the decode path and the gather engine read the [K, N] transpose
+            w.w_t = w.w_rot.t().contiguous()
+        if self.R > 0 and w.w_t is None:
+            raise RuntimeError("a tail needs the rotated bf16 weights (w_rot or w_t)")
+        self.w = w
+        self.small_m = int(small_m)
+        self.split_k = int(split_k)
+        self._ws = {}
+        self.activation_percentile = float(activation_percentile)
+        return self
+
+    def save(self, path, policy_entry: Optional[dict] = None) -> None:
+        """Writes the prepared weights (packed INT4, scales, rotated bf16 rows, bias) to a `.tqw` file."""
+        from . import weights_io
+        weights_io.save_prepared(path, self.w, ratio=self.ratio,
+                                 activation_percentile=getattr(self, "activation_percentile", 100.0),
+                                 policy_entry=policy_entry)
+
+    @classmethod
+    def load(cls, path, device="cuda", ratio: Optional[float] = None, tail_engine: str = "mma", small_m: int = 64,
+             split_k: int = 0, policy_entry: Optional[dict] = None) -> "SplitLinear":
+        """Reads a `.tqw` file; ratio and percentile default to the ones stored in it."""
+        from . import weights_io
+        h = weights_io.read_header(path)
+        w = weights_io.load_prepared(path, device, need_w_t=False, keep_w_rot=True, expect_policy_entry=policy_entry)
+        r = h.get("ratio") if ratio is None else ratio
+        return cls.from_prepared(w, ratio=0.0 if r is None else float(r),
+                                 activation_percentile=float(h.get("activation_percentile") or 100.0),
+                                 small_m=small_m, split_k=split_k, tail_engine=tail_engine)
 
     def _use_mma(self, M: int) -> bool:
         return self.tail_engine == "mma" and M > self.small_m

@@ -89,3 +89,22 @@ def select_params_for(entry: dict, K: int):
     R = ceil_ratio_count(K, float(entry["ratio"]))
     _, dr, _ = split_select_params(K, R, float(entry.get("activation_percentile", 100.0)))
     return R, dr
+
+
+def build_linears(named_weights: Dict[str, "object"], policy: dict, default_ratio: float = 0.0,
+                  tail_engine: str = "mma", min_ratio: float = 0.0):
+    """One `SplitLinear` per named weight with the ratio and percentile its policy entry gives
+    (`policy` as returned by `load_policy`; names as in the policy, e.g. "model.layers.3.mlp.down_proj").
+    Entries whose ratio is at most `min_ratio` take the pure W4A4 path (R = 0: no select, no tail operands) --
+    the adaptive bypass of tools/bench_qwen3_l18_split_opts_v59_adaptive.py:48-91.  Linears without an
+    entry get `default_ratio`."""
+    from .linear import SplitLinear
+    out = {}
+    for name, weight in named_weights.items():
+        entry = policy.get("modules", {}).get(normalize_name(name))
+        ratio = float(entry["ratio"]) if entry else float(default_ratio)
+        pct = float(entry["activation_percentile"]) if entry else 100.0
+        if ratio <= min_ratio:
+            ratio = 0.0
+        out[name] = SplitLinear(weight, ratio=ratio, activation_percentile=pct, tail_engine=tail_engine)
+    return out

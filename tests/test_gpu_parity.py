@@ -538,3 +538,43 @@ def test_full_size_properties_qwen3_layer_shapes():
         C = ops.matmul(out.a_pack, b_col)
         ref = torch._int_mm(codes.contiguous(), wq.t().contiguous())
         assert torch.equal(C, ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("engine,M", [("mma", 160), ("gather", 96), ("mma", 5)])
+def test_saved_prepared_weights_give_the_same_layer(tmp_path, engine, M):
+    """A layer written to a .tqw file and read back computes bit-identical outputs."""
+    from tailquant_kernel_b200 import SplitLinear
+    rng = np.random.default_rng(77)
+    K, N = 1024, 264
+    W = torch.from_numpy(rng.standard_normal((N, K)).astype(np.float32) * 0.02).to(torch.bfloat16).cuda()
+    bias = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16).cuda()
+    lin = SplitLinear(W, bias=bias, ratio=0.05, tail_engine=engine)
+    y0 = lin(x).clone()
+    lin.save(tmp_path / "l.tqw")
+    lin2 = SplitLinear.load(tmp_path / "l.tqw", tail_engine=engine)
+    assert (lin2.R, lin2.K, lin2.N, lin2.w.had_kind) == (lin.R, lin.K, lin.N, lin.w.had_kind)
+    y1 = lin2(x)
+    torch.cuda.synchronize()
+    assert torch.equal(y0, y1)
+
+
+@pytest.mark.gpu
+def test_policy_builds_layers_with_their_own_ratio():
+    from tailquant_kernel_b200 import policy
+    rng = np.random.default_rng(5)
+    K, N = 512, 136
+    names = ["model.layers.0.self_attn.o_proj", "model.layers.0.mlp.down_proj", "layers.1.mlp.up_proj"]
+    weights = {n: torch.from_numpy(rng.standard_normal((N, K)).astype(np.float32) * 0.02).to(torch.bfloat16).cuda()
+               for n in names}
+    pol = {"modules": {names[0]: {"ratio": 0.10, "activation_percentile": 100.0},
+                       names[1]: {"ratio": 0.004, "activation_percentile": 100.0}}}
+    lins = policy.build_linears(weights, pol, default_ratio=0.05, min_ratio=0.005)
+    assert lins[names[0]].R == 52 and lins[names[1]].R == 0 and lins[names[2]].R == 26
+    x = torch.from_numpy(rng.standard_normal((70, K)).astype(np.float32)).to(torch.bfloat16).cuda()
+    for n in names:  # every layer runs; the bypassed one equals a plain ratio-0 layer
+        y = lins[n](x)
+        assert y.shape == (70, N) and bool(torch.isfinite(y.float()).all())
+    from tailquant_kernel_b200 import SplitLinear
+    assert torch.equal(lins[names[1]](x), SplitLinear(weights[names[1]], ratio=0.0)(x))

@@ -164,3 +164,52 @@ def test_two_rank_row_sharding_gloo():
         assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     finally:
         os.unlink(f.name)
+
+
+# ------------------------------------------------------------------ prepared-weight file format (no GPU needed)
+def _toy_prepared(seed=0, N=24, K=128, bias=True, b_row=False):
+    import torch
+    from tailquant_kernel_b200 import ops
+    g = torch.Generator().manual_seed(seed)
+    return ops.PreparedWeight(
+        N, K, 1, torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g), torch.rand(N, generator=g), None,
+        torch.randint(0, 256, (K, N // 2), dtype=torch.uint8, generator=g) if b_row else None,
+        torch.randn((N, K), generator=g).to(torch.bfloat16), torch.rand(N, generator=g) if bias else None)
+
+
+def test_prepared_weight_file_round_trip(tmp_path):
+    import torch
+    from tailquant_kernel_b200 import weights_io
+    w = _toy_prepared(b_row=True)
+    path = tmp_path / "layer.tqw"
+    entry = {"ratio": 0.05, "activation_percentile": 100.0}
+    weights_io.save_prepared(path, w, ratio=0.05, policy_entry=entry)
+    h = weights_io.read_header(path)
+    assert (h["N"], h["K"], h["had_kind"], h["ratio"]) == (w.N, w.K, 1, 0.05)
+    assert all(t["offset"] % 256 == 0 for t in h["tensors"].values())
+    got = weights_io.load_prepared(path, "cpu", need_w_t=True, expect_policy_entry=entry)
+    for name in ("b_col", "w_scale", "w_rot", "b_row", "bias"):
+        assert torch.equal(getattr(got, name), getattr(w, name)), name
+    assert torch.equal(got.w_t, w.w_rot.t())
+    with pytest.raises(RuntimeError, match="another policy"):
+        weights_io.load_prepared(path, "cpu", expect_policy_entry={"ratio": 0.10, "activation_percentile": 100.0})
+
+
+def test_prepared_weight_file_rejects_damage(tmp_path):
+    from tailquant_kernel_b200 import weights_io
+    w = _toy_prepared(seed=1, bias=False)
+    path = tmp_path / "layer.tqw"
+    weights_io.save_prepared(path, w)
+    raw = bytearray(path.read_bytes())
+    off = weights_io.read_header(path)["tensors"]["b_col"]["offset"]
+    flipped = bytearray(raw)
+    flipped[off + 5] ^= 0x40
+    (tmp_path / "flip.tqw").write_bytes(flipped)
+    with pytest.raises(RuntimeError, match="checksum"):
+        weights_io.load_prepared(tmp_path / "flip.tqw", "cpu")
+    (tmp_path / "short.tqw").write_bytes(raw[: len(raw) // 2])
+    with pytest.raises(RuntimeError, match="outside the file|truncated"):
+        weights_io.load_prepared(tmp_path / "short.tqw", "cpu")
+    (tmp_path / "magic.tqw").write_bytes(b"NOPE" + bytes(raw[4:]))
+    with pytest.raises(RuntimeError, match="bad magic"):
+        weights_io.load_prepared(tmp_path / "magic.tqw", "cpu")
