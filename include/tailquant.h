@@ -71,12 +71,12 @@ const char* tq_last_cuda_error(void);
  *   tail_ld      row pitch (elements) of tail_idx16 / tail_val, >= R; idx32 / top_q are dense [M,R]
  *   tail_ptr     [M,ptr_ld] u16, ptr_ld >= K/128 + 1: tail_ptr[m][j] = number of tail entries of row m
  *                with index < 128 j (run boundaries for tq_split_gemm_mma; K % 128 == 0; may be NULL)
- *   tail_rec     [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
- *                tile and 128-wide K slice, entry j of the 128 rows contiguous -- what tq_split_gemm_mma
- *                reads, one coalesced load per j.  Entry = bf16 bits << 16 | (index & 64) | p, where
+ *   tail_rec     [ceil(M/128)][K/64][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
+ *                tile and 64-wide half of a K slice, entry j of the 128 rows contiguous -- what
+ *                tq_split_gemm_mma reads, one coalesced load per j.  Entry = bf16 bits << 16 | p, where
  *                p = ((((index & 63) >> 3) ^ (m & 7)) << 3) | (index & 7) is half the byte offset of the
  *                value in its 128-byte row of the 128-byte-swizzled operand tile (may be NULL)
- *   tail_cnt     [ceil(M/128)][K/128][128] u16 entries per (row, slice) (with tail_rec)
+ *   tail_cnt     [ceil(M/128)][K/64][128] u16 entries per (row, half slice) (with tail_rec)
  *   idx32        [M,R] i32 the same indices                          (T4; may be NULL)
  *   top_q        [M,R] i8  clamp(rint(x / top_scale), -8, 7)         (T4; may be NULL)
  *   x_rot        [M,K] bf16 rotated activations                      (debug / weight prep; may be NULL)
@@ -158,7 +158,7 @@ int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t
 
 /* tq_split_gemm_mma has two kernels: one CTA per 128 x 256 tile, and CTA pairs on 256 x 256 tiles
  * (tcgen05 cta_group::2; each CTA loads half of the weight tiles).  mode -1 (default) chooses by shape (pairs
- * without a tail, and with a tail for K < 8192 and M <= 4096), 0 / 1 force one of them.  A tuning knob without
+ * without a tail or when there are more than 74 one-CTA tiles), 0 / 1 force one of them.  A tuning knob without
  * a reference counterpart. */
 int tq_set_gemm_pair_mode(int mode);
 

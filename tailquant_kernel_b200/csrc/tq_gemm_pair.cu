@@ -37,8 +37,8 @@ struct PairGemmParams {
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
-  const uint32_t* rec;   // [tiles_m][K/128][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
-  const uint16_t* cnt;   // [tiles_m][K/128][128]: entries of the row in the slice
+  const uint32_t* rec;   // [tiles_m][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
+  const uint16_t* cnt;   // [tiles_m][K/64][128]: entries of the row in the 64-wide half slice
   const float* sx;
   const float* sw;
   const float* bias;
@@ -372,15 +372,18 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       const int btid = threadIdx.x - 6 * 32;
       const int brow = btid & 127, half = btid >> 7;
       const uint32_t roff = (uint32_t)((brow >> 3) * 1024 + (brow & 7) * 128);
-      const uint32_t halfbit = (uint32_t)half << 6;
-      // records and count of K slice g (over all tiles of the pair)
+      // records and count of this thread's 64-wide half of K slice g (g runs over all tiles of the pair), requested
+      // right after the previous fill.  This kernel runs at the 128-register cap and its builders sit on the
+      // critical path: ONE register set (a second set, or gating the loads on a count fetched earlier, spilled
+      // and measured 10-40 % slower), all sixteen records requested whatever the count is.
       auto fetch = [&](uint32_t(&r)[C], int& n, int g) {
         if (g < G) {
           const int i = g / kbt, kb = g - i * kbt;
           const int mt = 2 * tile_mt(i) + (int)rank;  // this CTA's 128-row tile
-          const uint32_t* recb = p.rec + ((size_t)mt * kbt + kb) * C * 128 + brow;
+          const size_t hs = ((size_t)mt * kbt + kb) * 2 + half;
+          const uint32_t* recb = p.rec + hs * C * 128 + brow;
           uint32_t n16;
-          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + ((size_t)mt * kbt + kb) * 128 + brow));
+          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + hs * 128 + brow));
           n = (int)n16;
 #pragma unroll
           for (int j = 0; j < C; ++j) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + (size_t)j * 128));
@@ -399,15 +402,19 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
 #pragma unroll
         for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
         if (brow == 0) TQ_TRACE(5, q, 2);
+        const int nmax = __reduce_max_sync(0xffffffffu, min(n, C));  // warp-uniform trip count
 #pragma unroll
         for (int j = 0; j < C; ++j) {
-          if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
-            *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
+          if (j < nmax) {
+            if (j < n) *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
+          }
         }
         if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
           const int i = g / kbt, kb = g - i * kbt;
           const size_t lrow = (size_t)(2 * tile_mt(i) + (int)rank) * P_BM + brow;
-          const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+          int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+          if (half)  // entries of the slice's first half
+            e0 += (int)__ldg(p.cnt + (((size_t)(2 * tile_mt(i) + (int)rank) * kbt + kb) * 2) * 128 + brow);
           const int lo = e0 + C, hi = e0 + n;  // list positions [lo, hi)
           const int kb0 = kb * P_BK + 64 * half;
           if ((p.ld & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.val)) & 15) == 0) {
@@ -449,19 +456,13 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
         if (g - i * kbt >= look - 1) catch_up(i);
         return ok;
       };
-      uint32_t ra[C], rb[C];
-      int na = 0, nb = 0;
+      uint32_t ra[C];
+      int na = 0;
       fetch(ra, na, 0);
-      fetch(rb, nb, 1);
-      for (int g = 0; g < G && ok; g += 2) {
+      for (int g = 0; g < G && ok; ++g) {
         ok = fill(g, ra, na) && after(g);
         if (!ok) break;
-        fetch(ra, na, g + 2);
-        if (g + 1 < G) {
-          ok = fill(g + 1, rb, nb) && after(g + 1);
-          if (!ok) break;
-          fetch(rb, nb, g + 3);
-        }
+        fetch(ra, na, g + 1);
       }
       catch_up(my_tiles);
     } else {

@@ -81,8 +81,8 @@ struct SplitGemmParams {
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
-  const uint32_t* rec;   // [tiles_m][K/128][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
-  const uint16_t* cnt;   // [tiles_m][K/128][128]: entries of the row in the slice
+  const uint32_t* rec;   // [tiles_m][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
+  const uint16_t* cnt;   // [tiles_m][K/64][128]: entries of the row in the 64-wide half slice
   const float* sx;
   const float* sw;
   const float* bias;
@@ -374,25 +374,27 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
       const int btid = threadIdx.x - 6 * 32;
       const int brow = btid & 127, half = btid >> 7;
       const uint32_t roff = (uint32_t)((brow >> 3) * 1024 + (brow & 7) * 128);
-      const uint32_t halfbit = (uint32_t)half << 6;
       bool ok = true;
       int q = 1 + half;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         const int mt = t % p.tiles_m;
         const int grow = mt * G_BM + brow;
-        const uint32_t* recb = p.rec + (size_t)mt * p.kb_total * C * 128 + brow;
-        const uint16_t* cntb = p.cnt + (size_t)mt * p.kb_total * 128 + brow;
-        auto fetch = [&](uint32_t(&r)[C], int& n, int kb) {
-          if (kb < p.kb_total) {
-            uint32_t n16;
-            asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 128));
-            n = (int)n16;
+        // records / counts of this thread's 64-wide half of every K slice of the tile
+        const uint32_t* recb = p.rec + ((size_t)mt * 2 * p.kb_total + half) * C * 128 + brow;
+        const uint16_t* cntb = p.cnt + ((size_t)mt * 2 * p.kb_total + half) * 128 + brow;
+        auto load_cnt = [&](int kb) -> int {
+          uint32_t n16 = 0u;
+          if (kb < p.kb_total) asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 256));
+          return (int)n16;
+        };
+        // `npre` holds the count of slice kb (loaded two fetches ago): only existing records are loaded; the
+        // count of slice kb + 2 is requested for the next fetch into this register set
+        auto fetch = [&](uint32_t(&r)[C], int& n, int& npre, int kb) {
+          n = npre;
 #pragma unroll
-            for (int j = 0; j < C; ++j)
-              asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + ((size_t)kb * C + j) * 128));
-          } else {
-            n = 0;
-          }
+          for (int j = 0; j < C; ++j)
+            if (j < n) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + ((size_t)kb * 2 * C + j) * 128));
+          npre = load_cnt(kb + 2);
         };
         auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {
           const int s = slot_of(q);
@@ -402,14 +404,17 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
           const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
+          const int nmax = __reduce_max_sync(0xffffffffu, min(n, C));  // warp-uniform trip count
 #pragma unroll
           for (int j = 0; j < C; ++j) {
-            if (j < n && ((r[j] ^ halfbit) & 64u) == 0u)
-              *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
+            if (j < nmax) {
+              if (j < n) *reinterpret_cast<uint16_t*>(arow + ((r[j] & 63u) << 1)) = (uint16_t)(r[j] >> 16);
+            }
           }
           if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
             const size_t lrow = (size_t)grow;
-            const int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+            int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
+            if (half) e0 += (int)__ldg(cntb - 128 + (size_t)kb * 256);  // entries of the slice's first half
             const int lo = e0 + C, hi = e0 + n;  // list positions [lo, hi)
             const int kb0 = kb * G_BK + 64 * half;
             if ((p.ld & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.val)) & 15) == 0) {
@@ -443,17 +448,17 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
           return true;
         };
         uint32_t ra[C], rb[C];
-        int na = 0, nb = 0;
-        fetch(ra, na, 0);
-        fetch(rb, nb, 1);
+        int na = 0, nb = 0, npa = load_cnt(0), npb = load_cnt(1);
+        fetch(ra, na, npa, 0);
+        fetch(rb, nb, npb, 1);
         for (int kb = 0; kb < p.kb_total && ok; kb += 2) {
           ok = fill(kb, ra, na);
           if (!ok) break;
-          fetch(ra, na, kb + 2);
+          fetch(ra, na, npa, kb + 2);
           if (kb + 1 < p.kb_total) {
             ok = fill(kb + 1, rb, nb);
             if (!ok) break;
-            fetch(rb, nb, kb + 3);
+            fetch(rb, nb, npb, kb + 3);
           }
         }
       }
@@ -572,11 +577,12 @@ extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, co
   if (M == 0) return TQ_OK;
   {
     // Choice between the one-CTA kernel (128 x 256 tiles) and the CTA-pair kernel (256 x 256 tiles, half the B
-    // traffic per CTA), from timings over M = 256..8192 on the Qwen3-8B and Llama-3-8B layer shapes: without a
-    // tail the pair kernel is 1.7-2x faster (two widening groups, epilogue shared by twelve warps); with a
-    // tail the two are within 5 % for K <= 8192 (pairs ahead up to M = 4096) and the one-CTA kernel is 20-30 %
-    // faster for the long-K projections.  TQ_GEMM_PAIR=0 / 1 or tq_set_gemm_pair_mode() force one of them.
-    const bool pair = g_gemm_pair_mode == 1 || (g_gemm_pair_mode < 0 && (R == 0 || (K < 8192 && M <= 4096)));
+    // traffic per CTA), from timings over M = 256..8192 on the Qwen3-8B and Llama-3-8B layer shapes: the pair
+    // kernel is 1.7-2x faster without a tail and 10-40 % faster with one, except for problems of at most 74
+    // one-CTA tiles (half a wave), where a tile's latency decides and the one-CTA kernel is 7-12 % ahead.
+    // TQ_GEMM_PAIR=0 / 1 or tq_set_gemm_pair_mode() force one of them.
+    const long tiles_single = (long)((M + 127) / 128) * ((N + 255) / 256);
+    const bool pair = g_gemm_pair_mode == 1 || (g_gemm_pair_mode < 0 && (R == 0 || tiles_single > 74));
     if (pair)
       return run_pair_gemm(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld,
                            tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, (cudaStream_t)stream);

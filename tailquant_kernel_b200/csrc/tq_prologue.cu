@@ -43,8 +43,8 @@ struct PrologueParams {
   uint16_t* tail_idx16;
   uint16_t* tail_val;
   uint16_t* tail_ptr;  // [M, ptr_ld]: entries with index < 128 * j, j = 0 .. K/128
-  uint32_t* tail_rec;  // [ceil(M/128)][K/128][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16
-  uint16_t* tail_cnt;  // [ceil(M/128)][K/128][128]: entries per 128-wide slice
+  uint32_t* tail_rec;  // [ceil(M/128)][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16
+  uint16_t* tail_cnt;  // [ceil(M/128)][K/64][128]: entries per 64-wide half slice
   int32_t* idx32;
   int8_t* top_q;
   uint16_t* x_rot;
@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
   constexpr int J = (GN + NT - 1) / NT;      // groups per thread: g = tid + NT * j
   constexpr int EJ = 8 * J;
   constexpr int NSL = K / 128;               // 128-wide slices (K % 128 == 0 for every built K)
+  constexpr int NHS = K / 64;                // 64-wide half slices: the unit of the tail records
   static_assert(J * (NT / 32) <= 64, "scan scratch");
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -247,9 +248,9 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
   int* res = reinterpret_cast<int*>(red + 32);
   uint32_t* scan_a = reinterpret_cast<uint32_t*>(res + 8);  // [J][8] warp totals, then their exclusive scan
   uint32_t* scan_b = scan_a + 64;
-  uint32_t* slice_pre = scan_b + 64;                         // [NSL] packed prefix at the start of each slice
+  uint32_t* slice_pre = scan_b + 64;                         // [NHS] packed prefix at the start of each half slice
   const int Rpad = (p.R + 7) & ~7;
-  uint16_t* st_idx = reinterpret_cast<uint16_t*>(slice_pre + ((NSL + 4) & ~3));
+  uint16_t* st_idx = reinterpret_cast<uint16_t*>(slice_pre + ((NHS + 4) & ~3));
   uint16_t* st_val = st_idx + Rpad;
   int8_t* st_q = reinterpret_cast<int8_t*>(st_val + Rpad);
 
@@ -424,7 +425,7 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
       for (int j = 0; j < J; ++j) {
         const int g = tid + NT * j;
         pre[j] = scan_b[j * (NT / 32) + warp] + incl[j] - cnt[j];
-        if (((GN % NT == 0) || g < GN) && (g & 15) == 0) slice_pre[g >> 4] = pre[j];
+        if (((GN % NT == 0) || g < GN) && (g & 7) == 0) slice_pre[g >> 3] = pre[j];
         tm[j] = mg[j];
         if (me[j]) {  // ties at the threshold: the `need` lowest indices of the row join the tail
           int neq = (int)(pre[j] >> 16);
@@ -438,19 +439,19 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
         }
       }
       __syncthreads();
-      // entries of the row's ascending list before a slice: the larger keys, plus the ties that made it
-      auto slice_start = [&](int sl) -> int {
-        const uint32_t ps = slice_pre[sl];
+      // entries of the row's ascending list before a half slice: the larger keys, plus the ties that made it
+      auto half_start = [&](int hs) -> int {
+        const uint32_t ps = slice_pre[hs];
         return (int)(ps & 0xffffu) + min((int)(ps >> 16), need);
       };
       if (p.tail_ptr) {  // run boundaries of the row's ascending index list at multiples of 128
         for (int sl = tid; sl <= NSL; sl += NT)
-          p.tail_ptr[(size_t)m * p.ptr_ld + sl] = (uint16_t)(sl < NSL ? slice_start(sl) : R);
+          p.tail_ptr[(size_t)m * p.ptr_ld + sl] = (uint16_t)(sl < NSL ? half_start(2 * sl) : R);
       }
       if (p.tail_cnt) {
-        for (int sl = tid; sl < NSL; sl += NT) {
-          const int ea = slice_start(sl), eb = sl + 1 < NSL ? slice_start(sl + 1) : R;
-          p.tail_cnt[((size_t)(m >> 7) * NSL + sl) * 128 + (m & 127)] = (uint16_t)(eb - ea);
+        for (int hs = tid; hs < NHS; hs += NT) {
+          const int ea = half_start(hs), eb = hs + 1 < NHS ? half_start(hs + 1) : R;
+          p.tail_cnt[((size_t)(m >> 7) * NHS + hs) * 128 + (m & 127)] = (uint16_t)(eb - ea);
         }
       }
       // ---- tail entries, ascending index order
@@ -468,13 +469,13 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
           const uint32_t vb = rowb[i];
           st_idx[pos] = (uint16_t)i;
           st_val[pos] = (uint16_t)vb;
-          if (p.tail_rec) {  // the entry's place in the record of its 128-wide slice
-            const int jr = pos - slice_start(i >> 7);
+          if (p.tail_rec) {  // the entry's place in the record of its 64-wide half slice
+            const int jr = pos - half_start(i >> 6);
             if (jr < TQ_TAIL_REC_CAP)
-              // bit 6: which 64-wide half; bits 0..5: half the byte offset of the value inside its
-              // 128-byte row of the swizzled operand tile (16-byte chunk index XOR row & 7, then the element)
-              p.tail_rec[(((size_t)(m >> 7) * NSL + (i >> 7)) * TQ_TAIL_REC_CAP + jr) * 128 + (m & 127)] =
-                  (uint32_t)(i & 64) | (uint32_t)(((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)) | (vb << 16);
+              // bits 0..5: half the byte offset of the value inside its 128-byte row of the swizzled operand
+              // tile (16-byte chunk index XOR row & 7, then the element); bits 16..31: the bf16 value
+              p.tail_rec[(((size_t)(m >> 7) * NHS + (i >> 6)) * TQ_TAIL_REC_CAP + jr) * 128 + (m & 127)] =
+                  (uint32_t)(((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)) | (vb << 16);
           }
           if (p.top_q) st_q[pos] = (int8_t)quant_s4(bf16_bits_to_f32(vb), tscale, trinv);
         }
@@ -528,7 +529,7 @@ template <int KIND, int K>
 int launch(const PrologueParams& p, cudaStream_t st) {
   auto kern = prologue_kernel<KIND, K>;
   const int Rpad = (p.R + 7) & ~7;
-  const size_t smem = (size_t)K * 6 + (128 + 32 + 8 + 64 + 64 + ((K / 128 + 4) & ~3)) * 4 + (size_t)Rpad * 5 + 16;
+  const size_t smem = (size_t)K * 6 + (128 + 32 + 8 + 64 + 64 + ((K / 64 + 4) & ~3)) * 4 + (size_t)Rpad * 5 + 16;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -26,9 +26,9 @@ class _Workspace:
             a_pack=None if q8 else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
             a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=device) if (mma and R) else None,
-            tail_rec=torch.empty(((M + 127) // 128, K // 128, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
+            tail_rec=torch.empty(((M + 127) // 128, K // 64, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
             if (mma and R) else None,
-            tail_cnt=torch.zeros(((M + 127) // 128, K // 128, 128), dtype=torch.int16, device=device)
+            tail_cnt=torch.zeros(((M + 127) // 128, K // 64, 128), dtype=torch.int16, device=device)
             if (mma and R) else None,
             body_scale=torch.empty(M, dtype=torch.float32, device=device),
             top_scale=torch.empty(M, dtype=torch.float32, device=device),

@@ -104,8 +104,8 @@ class PrologueOut:
     x_rot: Optional[torch.Tensor] = None  # [M, K] bf16
     a_q8: Optional[torch.Tensor] = None   # [M, K] i8, operand order of split_gemm_mma
     tail_ptr: Optional[torch.Tensor] = None  # [M, K/128 + 1] int16 storage of u16 run boundaries
-    tail_rec: Optional[torch.Tensor] = None  # [ceil(M/128), K/128, 16, 128] int32: (index & 127) | bf16 << 16
-    tail_cnt: Optional[torch.Tensor] = None  # [ceil(M/128), K/128, 128] int16: entries per (row, slice)
+    tail_rec: Optional[torch.Tensor] = None  # [ceil(M/128), K/64, 16, 128] int32: tile position | bf16 << 16
+    tail_cnt: Optional[torch.Tensor] = None  # [ceil(M/128), K/64, 128] int16: entries per (row, 64-wide half slice)
 
 
 def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
@@ -129,9 +129,9 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
             R=R,
             a_q8=torch.empty((M, K), dtype=torch.int8, device=dev) if want_q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=dev) if (want_q8 and R) else None,
-            tail_rec=torch.empty(((M + 127) // 128, K // 128, TAIL_REC_CAP, 128), dtype=torch.int32, device=dev)
+            tail_rec=torch.empty(((M + 127) // 128, K // 64, TAIL_REC_CAP, 128), dtype=torch.int32, device=dev)
             if (want_q8 and R) else None,
-            tail_cnt=torch.zeros(((M + 127) // 128, K // 128, 128), dtype=torch.int16, device=dev)
+            tail_cnt=torch.zeros(((M + 127) // 128, K // 64, 128), dtype=torch.int16, device=dev)
             if (want_q8 and R) else None,
             idx32=torch.empty((M, R), dtype=torch.int32, device=dev) if (t4 and R) else None,
             top_q=torch.empty((M, R), dtype=torch.int8, device=dev) if (t4 and R) else None,
@@ -293,8 +293,8 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
         _check_cuda(tail_rec, "tail_rec", torch.int32)
         _check_cuda(tail_cnt, "tail_cnt", torch.int16)
         _check(tail_ptr.shape[0] == M and tail_ptr.shape[1] >= K // 128 + 1, "tail_ptr must be [M, K/128 + 1]")
-        _check(tuple(tail_rec.shape) == ((M + 127) // 128, K // 128, TAIL_REC_CAP, 128), "tail_rec has the wrong shape")
-        _check(tuple(tail_cnt.shape) == ((M + 127) // 128, K // 128, 128), "tail_cnt has the wrong shape")
+        _check(tuple(tail_rec.shape) == ((M + 127) // 128, K // 64, TAIL_REC_CAP, 128), "tail_rec has the wrong shape")
+        _check(tuple(tail_cnt.shape) == ((M + 127) // 128, K // 64, 128), "tail_cnt has the wrong shape")
         ld = tail_idx.shape[1]
     if bias is not None:
         _check_cuda(bias, "bias", torch.float32)

@@ -280,22 +280,23 @@ def _output_bounds(y_bits, y32, slack=0.0):
 
 
 def tail_records(idx, val_bits, K, cap=16):
-    """The regrouped tail lists the fused GEMM reads: run boundaries, per-slice records and counts."""
+    """The regrouped tail lists the fused GEMM reads: run boundaries per 128-wide slice, records and counts per
+    64-wide half slice."""
     M, R = idx.shape
-    KB, TM = K // 128, (M + 127) // 128
-    bounds = np.arange(KB + 1, dtype=np.int64) * 128
-    ptr = np.stack([np.searchsorted(idx[m].astype(np.int64), bounds, side="left") for m in range(M)]).astype(np.uint16) \
-        if M else np.zeros((0, KB + 1), np.uint16)
-    rec = np.zeros((TM, KB, cap, 128), np.uint32)
-    cnt = np.zeros((TM, KB, 128), np.uint16)
+    KB, KH, TM = K // 128, K // 64, (M + 127) // 128
+    ptr = np.stack([np.searchsorted(idx[m].astype(np.int64), np.arange(KB + 1, dtype=np.int64) * 128, side="left")
+                    for m in range(M)]).astype(np.uint16) if M else np.zeros((0, KB + 1), np.uint16)
+    rec = np.zeros((TM, KH, cap, 128), np.uint32)
+    cnt = np.zeros((TM, KH, 128), np.uint16)
     for m in range(M):
-        for kb in range(KB):
-            a, b = int(ptr[m, kb]), int(ptr[m, kb + 1])
-            cnt[m >> 7, kb, m & 127] = b - a
+        hb = np.searchsorted(idx[m].astype(np.int64), np.arange(KH + 1, dtype=np.int64) * 64, side="left")
+        for h in range(KH):
+            a, b = int(hb[h]), int(hb[h + 1])
+            cnt[m >> 7, h, m & 127] = b - a
             for j in range(min(b - a, cap)):
                 i = int(idx[m, a + j])
-                pos = (i & 64) | ((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)
-                rec[m >> 7, kb, j, m & 127] = pos | (int(val_bits[m, a + j]) << 16)
+                pos = ((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)
+                rec[m >> 7, h, j, m & 127] = pos | (int(val_bits[m, a + j]) << 16)
     return ptr, rec, cnt
 
 
