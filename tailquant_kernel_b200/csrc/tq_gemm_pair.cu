@@ -376,17 +376,24 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       // right after the previous fill.  This kernel runs at the 128-register cap and its builders sit on the
       // critical path: ONE register set (a second set, or gating the loads on a count fetched earlier, spilled
       // and measured 10-40 % slower), all sixteen records requested whatever the count is.
-      auto fetch = [&](uint32_t(&r)[C], int& n, int g) {
-        if (g < G) {
-          const int i = g / kbt, kb = g - i * kbt;
-          const int mt = 2 * tile_mt(i) + (int)rank;  // this CTA's 128-row tile
-          const size_t hs = ((size_t)mt * kbt + kb) * 2 + half;
-          const uint32_t* recb = p.rec + hs * C * 128 + brow;
+      // (fi, fkb): local tile and slice of the NEXT slice to fetch, advanced without divisions -- this code runs
+      // between two fills; fhs: its position in the record arrays.
+      int fi = 0, fkb = 0;
+      size_t fhs = my_tiles > 0 ? ((size_t)(2 * tile_mt(0) + (int)rank) * kbt) * 2 + half : 0;
+      auto fetch = [&](uint32_t(&r)[C], int& n) {
+        if (fi < my_tiles) {
+          const uint32_t* recb = p.rec + fhs * C * 128 + brow;
           uint32_t n16;
-          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + hs * 128 + brow));
+          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + fhs * 128 + brow));
           n = (int)n16;
 #pragma unroll
           for (int j = 0; j < C; ++j) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + (size_t)j * 128));
+          fhs += 2;
+          if (++fkb == kbt) {  // next tile of the pair
+            fkb = 0;
+            ++fi;
+            if (fi < my_tiles) fhs = ((size_t)(2 * tile_mt(fi) + (int)rank) * kbt) * 2 + half;
+          }
         } else {
           n = 0;
         }
@@ -451,18 +458,22 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
         return true;
       };
       // a tile's epilogue share comes after the first slices of the next tile, as for the wideners
-      auto after = [&](int g) -> bool {
-        const int i = g / kbt;
-        if (g - i * kbt >= look - 1) catch_up(i);
+      int ci = 0, ckb = 0;  // local tile and slice of the slice just filled
+      auto after = [&]() -> bool {
+        if (ckb >= look - 1) catch_up(ci);
+        if (++ckb == kbt) {
+          ckb = 0;
+          ++ci;
+        }
         return ok;
       };
       uint32_t ra[C];
       int na = 0;
-      fetch(ra, na, 0);
+      fetch(ra, na);
       for (int g = 0; g < G && ok; ++g) {
-        ok = fill(g, ra, na) && after(g);
+        ok = fill(g, ra, na) && after();
         if (!ok) break;
-        fetch(ra, na, g + 1);
+        fetch(ra, na);
       }
       catch_up(my_tiles);
     } else {
