@@ -31,3 +31,51 @@ def column_shard(N: int, rank: int, world: int, multiple: int = 64) -> Tuple[int
         raise ValueError("N must be a multiple of the slab granularity")
     s, c = row_shard(N // multiple, rank, world)
     return s * multiple, c * multiple
+
+
+def gather_columns(y_local, N: int, group=None, multiple: int = 64):
+    """The one exchange step of the column-parallel split: every rank holds the [M, n_r] output slab of its
+    channels (`column_shard`) and receives the full [M, N] output.  One all-gather over the process group
+    (NCCL over NVLink on GPUs, gloo on CPU); slabs of unequal width are padded to the widest for the
+    collective and trimmed afterwards."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    shards = [column_shard(N, r, world, multiple) for r in range(world)]
+    M = y_local.shape[0]
+    if y_local.shape[1] != shards[rank][1]:
+        raise RuntimeError(f"rank {rank} holds {y_local.shape[1]} columns, its shard has {shards[rank][1]}")
+    widest = max(c for _, c in shards)
+    send = y_local
+    if send.shape[1] != widest:
+        send = torch.zeros((M, widest), dtype=y_local.dtype, device=y_local.device)
+        send[:, : y_local.shape[1]] = y_local
+    parts = [torch.empty((M, widest), dtype=y_local.dtype, device=y_local.device) for _ in range(world)]
+    dist.all_gather(parts, send.contiguous(), group=group)
+    out = torch.empty((M, N), dtype=y_local.dtype, device=y_local.device)
+    for (s0, c), part in zip(shards, parts):
+        out[:, s0:s0 + c] = part[:, :c]
+    return out
+
+
+class ColumnParallelSplitLinear:
+    """Optional N-split of one wide projection (e.g. gate_up): each rank prepares and runs the split linear on
+    its slab of output channels and the outputs are all-gathered.  Token-row sharding (no collective) stays the
+    default; this trades one exchange of M x N bf16 for 1/world of the weight traffic per GPU."""
+
+    def __init__(self, weight, rank: int, world: int, bias=None, group=None, multiple: int = 64, **kw):
+        from .linear import SplitLinear
+        self.N = int(weight.shape[0])
+        self.group, self.multiple = group, multiple
+        s0, c = column_shard(self.N, rank, world, multiple)
+        self.local = SplitLinear(weight[s0:s0 + c].contiguous(), bias=None if bias is None else bias[s0:s0 + c], **kw)
+
+    def forward(self, x):
+        y = self.local(x)
+        lead = y.shape[:-1]
+        full = gather_columns(y.reshape(-1, y.shape[-1]), self.N, self.group, self.multiple)
+        return full.view(*lead, self.N)
+
+    __call__ = forward

@@ -213,3 +213,40 @@ def test_prepared_weight_file_rejects_damage(tmp_path):
     (tmp_path / "magic.tqw").write_bytes(b"NOPE" + bytes(raw[4:]))
     with pytest.raises(RuntimeError, match="bad magic"):
         weights_io.load_prepared(tmp_path / "magic.tqw", "cpu")
+
+
+_COLUMN_WORKER = r"""
+import os, sys
+import torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from tailquant_kernel_b200.shard import column_shard, gather_columns
+dist.init_process_group("gloo", rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]))
+rank, world = dist.get_rank(), dist.get_world_size()
+M, N = 5, 7 * 64                       # 7 slabs of 64 columns over 2 ranks: 4 + 3, unequal widths
+full = (torch.arange(M * N, dtype=torch.float32).reshape(M, N) * 0.5).to(torch.bfloat16)
+s0, c = column_shard(N, rank, world)
+assert (s0, c) == ((0, 256) if rank == 0 else (256, 192))
+got = gather_columns(full[:, s0:s0 + c].contiguous(), N)
+assert got.dtype == torch.bfloat16 and torch.equal(got, full), "gathered columns differ"
+try:
+    gather_columns(full[:, :64].contiguous(), N)
+    raise SystemExit("a slab of the wrong width was accepted")
+except RuntimeError:
+    pass
+dist.barrier()
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_two_rank_column_gather_gloo():
+    with tempfile.NamedTemporaryFile("w", suffix=".py", delete=False) as f:
+        f.write(_COLUMN_WORKER)
+    try:
+        res = subprocess.run(
+            [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+             "--master-addr", "127.0.0.1", "--master-port", "29563", f.name, ROOT],
+            capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    finally:
+        os.unlink(f.name)
