@@ -39,9 +39,9 @@ RATIO = 0.05
 CPU_SAMPLE_ROWS = 64
 METRIC = "split W4A4+tail linear TOPS, Qwen3-8B layer shapes, prefill M=2048/GPU, ratio 0.05"
 NOMINAL_INT8_TOPS = 4500.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the three pair_gemm_kernel launches of one step (qkv, o, gate_up),
-# from the ncu capture summarised in profiles/pair_gemm_kernel_qwen3_layer_m2048.md (bytes)
-PAIR_GEMM_DRAM_BYTES_PER_STEP = int((269.0 + 85.0 + 76.8 + 9.3 + 54.9 + 4.3) * 1e6)
+# dram__bytes_read.sum + dram__bytes_write.sum of the four pair_gemm_kernel launches of one step (gate_up, down,
+# qkv, o), from the ncu capture summarised in profiles/pair_gemm_kernel_qwen3_layer_m2048.md (bytes)
+PAIR_GEMM_DRAM_BYTES_PER_STEP = int((279.1 + 86.0 + 235.3 + 13.6 + 81.1 + 9.5 + 59.5 + 2.2) * 1e6)
 
 
 def layer_ops(m: int) -> float:
@@ -385,11 +385,10 @@ def run_ours(args) -> None:
 
     h2d = sum(int(h.numel() * h.element_size()) for h in host_x)
     d2h = sum(int(h.numel() * h.element_size()) for h in host_y)
-    # The dominant kernel: with the tensor-core tail the three K = 4096 projections run on CTA pairs
-    # (pair_gemm_kernel), down_proj (K = 12288) on the one-CTA kernel; the roofline entry is the pair kernel's,
-    # summed over its three launches of a step.
+    # The dominant kernel: with the tensor-core tail all four projections of the layer run on CTA pairs
+    # (pair_gemm_kernel: each has more than 74 one-CTA tiles); the roofline entry sums its four launches of a step.
     if mma:
-        dom = [n for (n, K, N) in LAYER if K < 8192]
+        dom = [n for (n, K, N) in LAYER]
         kname = ("pair_gemm_kernel (tcgen05 cta_group::2: kind::i8 dense + kind::f16 tail, fused dequant); launches: "
                  + ", ".join(dom))
     else:
