@@ -532,7 +532,7 @@ def run_extra(args) -> None:
                 # one graph, so that every launch reads them from HBM and not from the 126 MB L2
                 def all_copies():
                     for b in b_copies:
-                        _ops.gemv_splitk(ws.pro.a_pack, b, ws.acc, 0)
+                        _ops.gemv_partials(ws.pro.a_pack, b, ws.acc)
                 t_gemm = graph_ms_of(all_copies) / len(b_copies)
                 t_pro = graph_ms_of(lambda: lin.prologue(x))
                 t_tail = graph_ms_of(lambda: _ops.tail_gather_small(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R))
@@ -540,7 +540,7 @@ def run_extra(args) -> None:
                 print(json.dumps({"workload": "decode", "linear": name, "M": M, "K": K, "N": N, "R": lin.R,
                                   "linear_ms": t_all, "splitk_gemm_ms": t_gemm,
                                   "prologue_ms": t_pro, "tail_gather_ms": t_tail,
-                                  "timing": "CUDA graph replay; splitk_gemm_ms = mean launch over %d weight copies "
+                                  "timing": "CUDA graph replay; splitk_gemm_ms = mean launch of the partial-sum GEMV over %d weight copies "
                                             "(HBM-resident), the other figures with L2-warm operands" % len(b_copies),
                                   "int4_weight_gbs": wbytes / (t_gemm * 1e-3) / 1e9,
                                   "frac_of_hbm_peak": wbytes / (t_gemm * 1e-3) / 1e9 / peaks["hbm_gbs"],

@@ -186,6 +186,15 @@ int tq_tail_gather(const uint16_t* tail_idx16, const void* tail_val, const void*
  *   interleaved fp32 fma chains (entry r on chain r mod 8) combined as ((c0+c1)+(c2+c3))+((c4+c5)+(c6+c7)). */
 int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* C, int M,
                         int N, int K, int split_k, void* stream);
+/* The same product with the K ranges kept apart: partials [splits, M, N] i32, slab s = the sum over K range s,
+ * every element written by plain stores (no zeroing, no atomics: one launch).  `splits` must be the count
+ * tq_int4_gemv_plan(M, N, K, a_is_int8) returns (> 0; negative = error code).
+ * tq_dequant_finish_partials adds the slabs (exactly) and finishes like tq_dequant_finish. */
+int tq_int4_gemv_plan(int M, int N, int K, int a_is_int8);
+int tq_int4_gemv_partials(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* partials,
+                          int M, int N, int K, int splits, void* stream);
+int tq_dequant_finish_partials(const int32_t* partials, int splits, const float* body_scale, const float* w_scale,
+                               const float* tail, const float* bias, void* out_bf16, int M, int N, void* stream);
 int tq_tail_gather_small(const uint16_t* tail_idx16, const void* tail_val, const void* w_t, float* tail,
                          int M, int N, int K, int R, int tail_ld, void* stream);
 

@@ -35,6 +35,9 @@ SIGNATURES = {
     "tq_idx_i32_to_u16": [_P, _P, _LL, _P],
     "tq_int4_linear_splitk_noalloc": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "tq_int4_gemv_splitk": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tq_int4_gemv_plan": [_I, _I, _I, _I],
+    "tq_int4_gemv_partials": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tq_dequant_finish_partials": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _P],
     "tq_tail_gather_small": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "tq_set_gemm_pair_mode": [_I],
     "tq_gemm_status": [_P],

@@ -50,13 +50,14 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 template <int MT, bool A8, bool SRC8>
 __global__ void __launch_bounds__(DV_THREADS)
 gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b_col, int32_t* __restrict__ C, int M,
-               int N, int K, int k_per_split, int direct, int cgroups) {
+               int N, int K, int k_per_split, int direct, int cgroups, long long pstride) {
   extern __shared__ __align__(16) unsigned char sm_a[];  // [16*MT rows][pitch] packed activations of this K range
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
   const int k0 = blockIdx.y * k_per_split;
   const int k1 = min(K, k0 + k_per_split);
   if (k0 >= k1) return;
+  C += (size_t)blockIdx.y * (size_t)pstride;  // partial-sum mode: one [M, N] slab per K range (pstride = M * N)
   static_assert(A8 || !SRC8, "INT8 input is staged as bytes");
   constexpr int AB = A8 ? 1 : 2;           // K elements per staged activation byte
   constexpr int SB = SRC8 ? 1 : 2;         // K elements per input byte
@@ -223,7 +224,7 @@ tail_small_kernel(const uint16_t* __restrict__ idx, const uint16_t* __restrict__
 
 template <int MT, bool A8, bool SRC8>
 int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, int N, int K, int kps, int splits,
-                int cgroups, cudaStream_t st) {
+                int cgroups, bool partials, cudaStream_t st) {
   const size_t smem = (size_t)16 * MT * (A8 ? kps + 16 : kps / 2 + 64);
   auto kern = gemv_s4_kernel<MT, A8, SRC8>;
   static bool configured[64] = {};
@@ -238,15 +239,70 @@ int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, 
     if (dev < 64) configured[dev] = true;
   }
   dim3 grid((N + DV_CH * cgroups - 1) / (DV_CH * cgroups), splits);
-  if (splits > 1) {  // partial sums of the K ranges meet in C through atomics
+  if (splits > 1 && !partials) {  // partial sums of the K ranges meet in C through atomics
     cudaError_t e = cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), st);
     if (e != cudaSuccess) {
       set_last_cuda_error(e);
       return TQ_ERR_CUDA;
     }
   }
-  kern<<<grid, DV_THREADS, smem, st>>>(a_pack, b_col, C, M, N, K, kps, splits == 1 ? 1 : 0, cgroups);
+  kern<<<grid, DV_THREADS, smem, st>>>(a_pack, b_col, C, M, N, K, kps, (splits == 1 || partials) ? 1 : 0, cgroups,
+                                             partials ? (long long)M * N : 0ll);
   return check_launch();
+}
+
+}  // namespace
+}  // namespace tq
+
+namespace tq {
+namespace {
+
+struct GemvPlan {
+  int sps, splits, mt, cgroups;
+};
+
+// K ranges of a call: `split_k` < 1 lets the library choose
+GemvPlan plan_gemv(int M, int N, int K, int split_k, bool a8) {
+  GemvPlan g;
+  const int slices = K / DV_KS;
+  g.mt = (M + 15) / 16;
+  // groups of 64 channels per CTA (sharing the staged activations): more than one measured slower at every M
+  // on the Qwen3-8B layer shapes -- the smaller grid costs more than the repeated staging
+  g.cgroups = 1;
+  if (split_k < 1) {  // four CTAs per SM, eight for the wide projections (timed on the Qwen3-8B layer shapes)
+    const int ctas_n = (N + DV_CH * g.cgroups - 1) / (DV_CH * g.cgroups);
+    split_k = ((ctas_n >= 256 ? 8 : 4) * 148 + ctas_n - 1) / ctas_n;
+  }
+  if (split_k > slices) split_k = slices;
+  g.sps = (slices + split_k - 1) / split_k;  // slices per split
+  // staged activation rows: at most 56 KB, four CTAs per SM
+  const int max_sps = (56 * 1024 / (16 * g.mt) - 64) / (a8 ? DV_KS : DV_KS / 2);
+  if (g.sps > max_sps) g.sps = max_sps;
+  g.splits = (slices + g.sps - 1) / g.sps;
+  return g;
+}
+
+int run_gemv(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* C, int M, int N, int K,
+             int split_k, bool partials, cudaStream_t st) {
+  if ((a_pack == nullptr) == (a_q8 == nullptr) || !b_col || !C || M < 0 || N <= 0 || K <= 0) return TQ_ERR_BAD_ARG;
+  if (M > 64 || K % DV_KS != 0) return TQ_ERR_UNSUPPORTED;
+  const bool a8 = a_q8 != nullptr;
+  const uint8_t* a = a8 ? reinterpret_cast<const uint8_t*>(a_q8) : a_pack;
+  if (!aligned16(a) || !aligned16(b_col)) return TQ_ERR_MISALIGNED;
+  if (M == 0) return TQ_OK;
+  const GemvPlan g = plan_gemv(M, N, K, split_k, a8);
+  if (partials && split_k >= 1 && g.splits != split_k) return TQ_ERR_BAD_ARG;  // the slab count must be the caller's
+  const int kps = g.sps * DV_KS, splits = g.splits, cgroups = g.cgroups, mt = g.mt;
+  if (a8) {
+    if (mt == 1) return launch_gemv<1, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    if (mt == 2) return launch_gemv<2, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    if (mt == 3) return launch_gemv<3, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    return launch_gemv<4, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+  }
+  if (mt == 1) return launch_gemv<1, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+  if (mt == 2) return launch_gemv<2, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+  if (mt == 3) return launch_gemv<3, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+  return launch_gemv<4, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
 }
 
 }  // namespace
@@ -254,41 +310,18 @@ int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, 
 
 extern "C" int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* C, int M,
                                    int N, int K, int split_k, void* stream) {
-  using namespace tq;
-  if ((a_pack == nullptr) == (a_q8 == nullptr) || !b_col || !C || M < 0 || N <= 0 || K <= 0) return TQ_ERR_BAD_ARG;
-  if (M > 64 || K % DV_KS != 0) return TQ_ERR_UNSUPPORTED;
-  const bool a8 = a_q8 != nullptr;
-  const uint8_t* a = a8 ? reinterpret_cast<const uint8_t*>(a_q8) : a_pack;
-  if (!aligned16(a) || !aligned16(b_col)) return TQ_ERR_MISALIGNED;
-  if (M == 0) return TQ_OK;
-  cudaStream_t st = (cudaStream_t)stream;
-  const int slices = K / DV_KS;
-  const int mt = (M + 15) / 16;
-  // groups of 64 channels per CTA (sharing the staged activations): more than one measured slower at every M
-  // on the Qwen3-8B layer shapes -- the smaller grid costs more than the repeated staging
-  const int cgroups = 1;
-  if (split_k < 1) {  // four CTAs per SM, eight for the wide projections (timed on the Qwen3-8B layer shapes)
-    const int ctas_n = (N + DV_CH * cgroups - 1) / (DV_CH * cgroups);
-    split_k = ((ctas_n >= 256 ? 8 : 4) * 148 + ctas_n - 1) / ctas_n;
-  }
-  if (split_k > slices) split_k = slices;
-  int sps = (slices + split_k - 1) / split_k;                 // slices per split
-  const bool bytes_staged = a8;
-  // staged activation rows: at most 56 KB, four CTAs per SM
-  const int max_sps = (56 * 1024 / (16 * mt) - 64) / (bytes_staged ? DV_KS : DV_KS / 2);
-  if (sps > max_sps) sps = max_sps;
-  const int splits = (slices + sps - 1) / sps;
-  const int kps = sps * DV_KS;
-  if (a8) {
-    if (mt == 1) return launch_gemv<1, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-    if (mt == 2) return launch_gemv<2, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-    if (mt == 3) return launch_gemv<3, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-    return launch_gemv<4, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-  }
-  if (mt == 1) return launch_gemv<1, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-  if (mt == 2) return launch_gemv<2, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-  if (mt == 3) return launch_gemv<3, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
-  return launch_gemv<4, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, st);
+  return tq::run_gemv(a_pack, a_q8, b_col, C, M, N, K, split_k, false, (cudaStream_t)stream);
+}
+
+extern "C" int tq_int4_gemv_plan(int M, int N, int K, int a_is_int8) {
+  if (M < 1 || M > 64 || N <= 0 || K <= 0 || K % tq::DV_KS != 0) return TQ_ERR_BAD_ARG;
+  return tq::plan_gemv(M, N, K, 0, a_is_int8 != 0).splits;
+}
+
+extern "C" int tq_int4_gemv_partials(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* partials,
+                                     int M, int N, int K, int splits, void* stream) {
+  if (splits < 1) return TQ_ERR_BAD_ARG;
+  return tq::run_gemv(a_pack, a_q8, b_col, partials, M, N, K, splits, true, (cudaStream_t)stream);
 }
 
 extern "C" int tq_tail_gather_small(const uint16_t* tail_idx16, const void* tail_val, const void* w_t, float* tail,

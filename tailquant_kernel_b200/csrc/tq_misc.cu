@@ -52,6 +52,22 @@ __global__ void dequant_finish_kernel(const int32_t* __restrict__ C, const float
   out[i] = (uint16_t)f32_to_bf16_bits(d);
 }
 
+// the same with the accumulators still split over `splits` K ranges ([splits, M, N]): summed here, exactly
+__global__ void dequant_finish_partials_kernel(const int32_t* __restrict__ P, int splits, const float* __restrict__ sx,
+                                               const float* __restrict__ sw, const float* __restrict__ tail,
+                                               const float* __restrict__ bias, uint16_t* __restrict__ out, int M, int N) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)M * N;
+  if (i >= total) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  int acc = 0;
+  for (int s = 0; s < splits; ++s) acc += P[(size_t)s * total + i];
+  float d = __fmul_rn(__fmul_rn((float)acc, sx[m]), sw[n]);
+  if (tail) d = __fadd_rn(d, tail[i]);
+  if (bias) d = __fadd_rn(d, bias[n]);
+  out[i] = (uint16_t)f32_to_bf16_bits(d);
+}
+
 // ------------------------------------------------------------------ T4 sparse term
 __device__ __forceinline__ int s4(uint32_t nib) { return (int)((nib & 0xfu) ^ 8u) - 8; }
 
@@ -156,6 +172,17 @@ extern "C" int tq_dequant_finish(const int32_t* C, const float* body_scale, cons
   const size_t total = (size_t)M * N;
   tq::dequant_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       C, body_scale, w_scale, tail, bias, reinterpret_cast<uint16_t*>(out_bf16), M, N);
+  return tq::check_launch();
+}
+
+extern "C" int tq_dequant_finish_partials(const int32_t* partials, int splits, const float* body_scale,
+                                          const float* w_scale, const float* tail, const float* bias, void* out_bf16,
+                                          int M, int N, void* stream) {
+  if (!partials || splits < 1 || !body_scale || !w_scale || !out_bf16 || M < 0 || N <= 0) return TQ_ERR_BAD_ARG;
+  if (M == 0) return TQ_OK;
+  const size_t total = (size_t)M * N;
+  tq::dequant_finish_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      partials, splits, body_scale, w_scale, tail, bias, reinterpret_cast<uint16_t*>(out_bf16), M, N);
   return tq::check_launch();
 }
 

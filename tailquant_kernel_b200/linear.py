@@ -147,10 +147,11 @@ class SplitLinear:
         if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
             if self.R:
                 ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
-            if ws.acc is None:
-                ws.acc = torch.empty((M, self.N), dtype=torch.int32, device=ws.out.device)
-            ops.gemv_splitk(pro.a_pack, w.b_col, ws.acc, self.split_k)
-            ops.dequant_finish(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
+            if ws.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
+                splits = ops.gemv_plan(M, self.N, self.K)
+                ws.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=ws.out.device)
+            ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
+            ops.dequant_finish_partials(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
             return ws.out
         if self.R:
             ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)

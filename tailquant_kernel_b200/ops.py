@@ -340,6 +340,44 @@ def gemv_splitk(A, B_pack, C: torch.Tensor, split_k: int = 0) -> torch.Tensor:
     return C
 
 
+def gemv_plan(M: int, N: int, K: int, a_is_int8: bool = False) -> int:
+    """Number of K ranges the library uses for the decode GEMV of this shape (= leading size of the partials)."""
+    n = _lib.load().tq_int4_gemv_plan(int(M), int(N), int(K), 1 if a_is_int8 else 0)
+    if n < 1:
+        _lib.check(n, f"gemv_plan(M={M}, N={N}, K={K})")
+    return int(n)
+
+
+def gemv_partials(A, B_pack, partials: torch.Tensor) -> torch.Tensor:
+    """Decode GEMV with the K ranges kept apart: partials [splits, M, N] int32 (splits = gemv_plan(...)),
+    written by plain stores in one launch; `dequant_finish_partials` adds them up."""
+    _check_cuda(A, "A")
+    _check_cuda(B_pack, "B_pack", torch.uint8)
+    _check(A.dtype in (torch.uint8, torch.int8) and A.dim() == 2, "A must be uint8 [M,K/2] or int8 [M,K]")
+    a8 = A.dtype == torch.int8
+    M, N, K = A.shape[0], B_pack.shape[0], B_pack.shape[1] * 2
+    _check(A.shape[1] == (K if a8 else K // 2), "A and B_pack disagree on K")
+    _check_cuda(partials, "partials", torch.int32)
+    _check(partials.dim() == 3 and tuple(partials.shape[1:]) == (M, N), "partials must be [splits, M, N]")
+    rc = _lib.load().tq_int4_gemv_partials(None if a8 else _ptr(A), _ptr(A) if a8 else None, _ptr(B_pack),
+                                           _ptr(partials), M, N, K, int(partials.shape[0]), _stream())
+    _lib.check(rc, f"gemv_partials(M={M}, N={N}, K={K}, splits={partials.shape[0]})")
+    return partials
+
+
+def dequant_finish_partials(partials, body_scale, w_scale, out, tail=None, bias=None):
+    """out = bf16((float(sum_s partials[s]) * body_scale[m]) * w_scale[n] + tail + bias)."""
+    _check_cuda(partials, "partials", torch.int32)
+    _check(partials.dim() == 3, "partials must be [splits, M, N]")
+    S, M, N = partials.shape
+    _check_cuda(out, "out", torch.bfloat16)
+    _check(out.numel() >= M * N, "out too small")
+    rc = _lib.load().tq_dequant_finish_partials(_ptr(partials), int(S), _ptr(body_scale), _ptr(w_scale), _ptr(tail),
+                                                _ptr(bias), _ptr(out), M, N, _stream())
+    _lib.check(rc, f"dequant_finish_partials(S={S}, M={M}, N={N})")
+    return out
+
+
 def tail_gather_small(tail_idx, tail_val, w_t, tail_out, R: int):
     """Tail sums for few rows (decode): gathers only the needed weight rows; eight interleaved fp32 chains per
     output combined pairwise in a fixed order."""

@@ -579,3 +579,33 @@ def test_policy_builds_layers_with_their_own_ratio():
         assert y.shape == (70, N) and bool(torch.isfinite(y.float()).all())
     from tailquant_kernel_b200 import SplitLinear
     assert torch.equal(lins[names[1]](x), SplitLinear(weights[names[1]], ratio=0.0)(x))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 520, 1024), (33, 264, 12288), (64, 6144, 512), (5, 8, 128)])
+def test_gemv_partials_and_finisher(M, N, K):
+    """Partial sums per K range add up to the exact product; the finisher over partials equals the finisher
+    over the summed accumulators bit for bit."""
+    rng = np.random.default_rng(M * 7 + N + K)
+    g = lambda a: torch.from_numpy(a).cuda()
+    qa, qw = rand_codes(rng, M, K), rand_codes(rng, N, K)
+    A, B = g(O.pack_s4(qa)), g(O.pack_s4(qw))
+    splits = ops.gemv_plan(M, N, K)
+    assert 1 <= splits <= K // 128
+    P = torch.full((splits, M, N), 12345, dtype=torch.int32, device="cuda")   # every element must be overwritten
+    ops.gemv_partials(A, B, P)
+    total = P.sum(dim=0, dtype=torch.int64).cpu().numpy()
+    assert np.array_equal(total, O.int_gemm(qa, qw).astype(np.int64))
+    sx = g(rng.uniform(0.01, 0.2, M).astype(np.float32))
+    sw = g(rng.uniform(0.001, 0.01, N).astype(np.float32))
+    tail = g(rng.standard_normal((M, N)).astype(np.float32))
+    bias = g(rng.standard_normal(N).astype(np.float32))
+    C = P.sum(dim=0, dtype=torch.int32)
+    out_a = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    out_b = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    ops.dequant_finish(C, sx, sw, out_a, tail=tail, bias=bias)
+    ops.dequant_finish_partials(P, sx, sw, out_b, tail=tail, bias=bias)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b)
+    with pytest.raises(RuntimeError):  # a slab count the plan does not give
+        ops.gemv_partials(A, B, torch.empty((K // 128 + 3, M, N), dtype=torch.int32, device="cuda"))
