@@ -18,6 +18,17 @@ import torch
 from . import ops
 
 
+_SIDE: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _SIDE.get(idx)
+    if st is None:
+        st = _SIDE[idx] = torch.cuda.Stream(device=idx)
+    return st
+
+
 class _Workspace:
     def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool):
         ld = (R + 7) // 8 * 8
@@ -36,8 +47,10 @@ class _Workspace:
             tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=device) if R else None,
             R=R)
         self.tail = torch.empty((M, N), dtype=torch.float32, device=device) if (R and not mma) else None
-        self.acc = None  # int32 [M, N], split-K path only
+        self.acc = None  # int32 [splits, M, N], decode path only
         self.out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        if small and R:
+            self.ev_fork, self.ev_join = torch.cuda.Event(), torch.cuda.Event()
 
 
 class SplitLinear:
@@ -145,12 +158,23 @@ class SplitLinear:
             return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot, pro=pro,
                                       R=self.R, bias=w.bias)
         if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
-            if self.R:
-                ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
             if ws.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
                 splits = ops.gemv_plan(M, self.N, self.K)
                 ws.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=ws.out.device)
-            ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
+            if self.R:
+                # the tail sums and the GEMV only depend on the prologue and neither fills the GPU at these sizes:
+                # the tail runs on a side stream next to the GEMV (a parallel branch when captured in a CUDA graph)
+                cur = torch.cuda.current_stream()
+                side = _side_stream(ws.out.device)
+                ws.ev_fork.record(cur)
+                side.wait_event(ws.ev_fork)
+                with torch.cuda.stream(side):
+                    ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
+                    ws.ev_join.record(side)
+                ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
+                cur.wait_event(ws.ev_join)
+            else:
+                ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
             ops.dequant_finish_partials(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
             return ws.out
         if self.R:
