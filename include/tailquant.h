@@ -71,12 +71,14 @@ const char* tq_last_cuda_error(void);
  *   tail_ld      row pitch (elements) of tail_idx16 / tail_val, >= R; idx32 / top_q are dense [M,R]
  *   tail_ptr     [M,ptr_ld] u16, ptr_ld >= K/128 + 1: tail_ptr[m][j] = number of tail entries of row m
  *                with index < 128 j (run boundaries for tq_split_gemm_mma; K % 128 == 0; may be NULL)
- *   tail_rec     [ceil(M/128)][K/64][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
+ *   tail_rec     [2 ceil(M/256)][K/64][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
  *                tile and 64-wide half of a K slice, entry j of the 128 rows contiguous -- what
  *                tq_split_gemm_mma reads, one coalesced load per j.  Entry = bf16 bits << 16 | p, where
  *                p = ((((index & 63) >> 3) ^ (m & 7)) << 3) | (index & 7) is half the byte offset of the
  *                value in its 128-byte row of the 128-byte-swizzled operand tile (may be NULL)
- *   tail_cnt     [ceil(M/128)][K/64][128] u16 entries per (row, half slice) (with tail_rec)
+ *   tail_cnt     [2 ceil(M/256)][K/64][128] u16 entries per (row, half slice) (with tail_rec); the rows that
+ *                pad M to a multiple of 256 are written as 0 (both arrays cover them: the CTA-pair GEMM
+ *                works on 256-row tiles and does not check rows)
  *   idx32        [M,R] i32 the same indices                          (T4; may be NULL)
  *   top_q        [M,R] i8  clamp(rint(x / top_scale), -8, 7)         (T4; may be NULL)
  *   x_rot        [M,K] bf16 rotated activations                      (debug / weight prep; may be NULL)
@@ -156,6 +158,18 @@ int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t
                       const float* bias, void* out_bf16,
                       int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream);
 
+/* The same linear for a fused gate_up projection whose weight rows are INTERLEAVED (row 2i = gate_i, row 2i+1 =
+ * up_i; N = 2 I): the epilogue applies SwiGLU to each channel pair and writes out [M, N/2] bf16,
+ *   out[m,i] = bf16( bf16(silu(g)) * u ),  g = bf16(y[m,2i]), u = bf16(y[m,2i+1]),  silu(g) = g / (1 + exp(-g)),
+ * i.e. what a bf16 framework computes from the two linears' bf16 outputs -- the reference does this step in
+ * PyTorch (tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:214).  No [M, N]
+ * intermediate is written. */
+int tq_split_gemm_mma_swiglu(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
+                             const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
+                             const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
+                             const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
+                             const float* bias, void* out_bf16, int M, int N, int K, void* stream);
+
 /* tq_split_gemm_mma has two kernels: one CTA per 128 x 256 tile, and CTA pairs on 256 x 256 tiles
  * (tcgen05 cta_group::2; each CTA loads half of the weight tiles).  mode -1 (default) chooses by shape (pairs
  * without a tail or when there are more than 74 one-CTA tiles), 0 / 1 force one of them.  A tuning knob without
@@ -189,12 +203,14 @@ int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t
 /* The same product with the K ranges kept apart: partials [splits, M, N] i32, slab s = the sum over K range s,
  * every element written by plain stores (no zeroing, no atomics: one launch).  `splits` must be the count
  * tq_int4_gemv_plan(M, N, K, a_is_int8) returns (> 0; negative = error code).
- * tq_dequant_finish_partials adds the slabs (exactly) and finishes like tq_dequant_finish. */
+ * tq_dequant_finish_partials adds the slabs (exactly) and finishes like tq_dequant_finish; act = 1 applies the
+ * SwiGLU of tq_split_gemm_mma_swiglu (out [M, N/2]). */
 int tq_int4_gemv_plan(int M, int N, int K, int a_is_int8);
 int tq_int4_gemv_partials(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* partials,
                           int M, int N, int K, int splits, void* stream);
 int tq_dequant_finish_partials(const int32_t* partials, int splits, const float* body_scale, const float* w_scale,
-                               const float* tail, const float* bias, void* out_bf16, int M, int N, void* stream);
+                               const float* tail, const float* bias, void* out_bf16, int M, int N, int act,
+                               void* stream);
 int tq_tail_gather_small(const uint16_t* tail_idx16, const void* tail_val, const void* w_t, float* tail,
                          int M, int N, int K, int R, int tail_ld, void* stream);
 

@@ -367,6 +367,19 @@ def split_linear_t16(x_bits: np.ndarray, w: PreparedWeight, kind: int, R: int,
     return f32_to_bf16_bits(y), y, p, acc
 
 
+def swiglu_bf16(y_bits: np.ndarray) -> np.ndarray:
+    """SwiGLU over interleaved (gate, up) columns of a bf16 matrix [M, 2I] -> bf16 bits [M, I], evaluated the way
+    a bf16 framework does on the two linears' outputs (the reference computes act(gate) * up in PyTorch,
+    tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:214): silu(g) = g / (1 + exp(-g))
+    in fp32, rounded to bf16, times up, rounded to bf16."""
+    g = bf16_bits_to_f32(y_bits[:, 0::2])
+    u = bf16_bits_to_f32(y_bits[:, 1::2])
+    with np.errstate(over="ignore"):
+        e = np.exp(-g, dtype=np.float32)
+    s = bf16_bits_to_f32(f32_to_bf16_bits((g / (np.float32(1.0) + e)).astype(np.float32)))
+    return f32_to_bf16_bits((s * u).astype(np.float32))
+
+
 def sparse_int_t4(top_q: np.ndarray, idx: np.ndarray, w_codes: np.ndarray) -> np.ndarray:
     """sum_r top_q[m,r] * qw[n, idx[m,r]] in int32 (tools/fused_sparse_epilogue_ext_v58.py:59-74)."""
     M, R = idx.shape

@@ -23,6 +23,7 @@ SIGNATURES = {
     "tq_last_cuda_error": [],
     "tq_split_prologue": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
     "tq_split_gemm_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "tq_split_gemm_mma_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "tq_topr_pack": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P],
     "tq_prepare_weight": [_P, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P],
     "tq_int4_matmul": [_P, _P, _P, _I, _I, _I, _I, _P],
@@ -37,7 +38,7 @@ SIGNATURES = {
     "tq_int4_gemv_splitk": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "tq_int4_gemv_plan": [_I, _I, _I, _I],
     "tq_int4_gemv_partials": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "tq_dequant_finish_partials": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _P],
+    "tq_dequant_finish_partials": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "tq_tail_gather_small": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "tq_set_gemm_pair_mode": [_I],
     "tq_gemm_status": [_P],

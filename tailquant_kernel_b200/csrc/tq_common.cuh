@@ -28,6 +28,16 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
 
+// SwiGLU of one (gate, up) pair the way a bf16 framework evaluates it on the two linears' bf16 outputs
+// (the reference computes act(gate) * up in PyTorch: tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:214):
+// both inputs rounded to bf16, silu(g) = g / (1 + exp(-g)) in fp32 rounded to bf16, product rounded to bf16.
+__device__ __forceinline__ uint32_t swiglu_bf16_bits(float g, float u) {
+  g = bf16_bits_to_f32(f32_to_bf16_bits(g));
+  u = bf16_bits_to_f32(f32_to_bf16_bits(u));
+  const float s = bf16_bits_to_f32(f32_to_bf16_bits(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g)))));
+  return f32_to_bf16_bits(__fmul_rn(s, u));
+}
+
 // clamp(rint(x / scale), -8, 7) with true fp32 division semantics.  The product with the
 // reciprocal decides every case that is not within 1e-3 of a rounding boundary (its error
 // is below 2e-6 for |t| < 16, and beyond that both evaluations clamp to the same side);

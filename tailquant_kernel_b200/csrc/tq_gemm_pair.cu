@@ -37,8 +37,8 @@ struct PairGemmParams {
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
-  const uint32_t* rec;   // [tiles_m][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
-  const uint16_t* cnt;   // [tiles_m][K/64][128]: entries of the row in the 64-wide half slice
+  const uint32_t* rec;   // [2 tiles_m][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
+  const uint16_t* cnt;   // [2 tiles_m][K/64][128]: entries of the row in the 64-wide half slice (0 for rows >= M)
   const float* sx;
   const float* sw;
   const float* bias;
@@ -68,6 +68,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+template <int ACT>  // 0: out [M, N]; 1: SwiGLU over interleaved (gate, up) channel pairs, out [M, N/2]
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_constant__ CUtensorMap tmap_b4,
                   const __grid_constant__ CUtensorMap tmap_w, const PairGemmParams p) {
@@ -180,12 +181,19 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
 #pragma unroll
             for (int k = 0; k < 8; ++k) d[k] = __fadd_rn(d[k], bs[k]);
           }
-          uint4 o;
-          o.x = pack_bf16x2(d[0], d[1]);
-          o.y = pack_bf16x2(d[2], d[3]);
-          o.z = pack_bf16x2(d[4], d[5]);
-          o.w = pack_bf16x2(d[6], d[7]);
-          *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+          if (ACT) {
+            uint2 o;
+            o.x = swiglu_bf16_bits(d[0], d[1]) | (swiglu_bf16_bits(d[2], d[3]) << 16);
+            o.y = swiglu_bf16_bits(d[4], d[5]) | (swiglu_bf16_bits(d[6], d[7]) << 16);
+            *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.N + n) / 2) = o;
+          } else {
+            uint4 o;
+            o.x = pack_bf16x2(d[0], d[1]);
+            o.y = pack_bf16x2(d[2], d[3]);
+            o.z = pack_bf16x2(d[4], d[5]);
+            o.w = pack_bf16x2(d[6], d[7]);
+            *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+          }
           if (p.dbg_acc) {
             *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n) =
                 make_int4((int)ri[8 * j] >> 4, (int)ri[8 * j + 1] >> 4, (int)ri[8 * j + 2] >> 4, (int)ri[8 * j + 3] >> 4);
@@ -379,6 +387,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       // (fi, fkb): local tile and slice of the NEXT slice to fetch, advanced without divisions -- this code runs
       // between two fills; fhs: its position in the record arrays.
       int fi = 0, fkb = 0;
+      // (The record arrays cover 2 * ceil(M / 256) row tiles, and rows at or beyond M have zero counts: no bounds
+      // checks here.)
       size_t fhs = my_tiles > 0 ? ((size_t)(2 * tile_mt(0) + (int)rank) * kbt) * 2 + half : 0;
       auto fetch = [&](uint32_t(&r)[C], int& n) {
         if (fi < my_tiles) {
@@ -418,7 +428,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
         }
         if (n > C) {  // a run longer than the record: the rest comes from the row's sorted list, 8 entries a load
           const int i = g / kbt, kb = g - i * kbt;
-          const size_t lrow = (size_t)(2 * tile_mt(i) + (int)rank) * P_BM + brow;
+          const size_t lrow = (size_t)(2 * tile_mt(i) + (int)rank) * P_BM + brow;  // < M: other rows have zero counts
           int e0 = (int)__ldg(p.ptr + lrow * p.ptr_ld + kb);
           if (half)  // entries of the slice's first half
             e0 += (int)__ldg(p.cnt + (((size_t)(2 * tile_mt(i) + (int)rank) * kbt + kb) * 2) * 128 + brow);
@@ -497,13 +507,14 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
   }
 }
 
+template <int ACT>
 int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot, PairGemmParams p, cudaStream_t st) {
   using S = PS;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(dev < 64 && configured[dev])) {
-    cudaError_t e = cudaFuncSetAttribute(pair_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN);
+    cudaError_t e = cudaFuncSetAttribute(pair_gemm_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN);
     if (e != cudaSuccess) {
       set_last_cuda_error(e);
       return TQ_ERR_CUDA;
@@ -528,7 +539,7 @@ int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int total = p.tiles_m * p.tiles_n;
   const int pairs = total < sms / 2 ? total : sms / 2;
-  pair_gemm_kernel<<<2 * pairs, P_THREADS, S::DYN, st>>>(ma, mb, mw, p);
+  pair_gemm_kernel<ACT><<<2 * pairs, P_THREADS, S::DYN, st>>>(ma, mb, mw, p);
   return check_launch();
 }
 
@@ -538,7 +549,7 @@ int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot
 int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
                   const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
                   const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
-                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K,
+                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, int act,
                   cudaStream_t st) {
   PairGemmParams p = {};
   p.M = M;
@@ -559,7 +570,7 @@ int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_
   p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
   p.dbg_acc = dbg_acc;
   p.dbg_tail = dbg_tail;
-  return launch_pair_gemm(a_q8, b_col, w_rot, p, st);
+  return act ? launch_pair_gemm<1>(a_q8, b_col, w_rot, p, st) : launch_pair_gemm<0>(a_q8, b_col, w_rot, p, st);
 }
 
 }  // namespace tq

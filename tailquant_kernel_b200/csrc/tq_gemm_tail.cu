@@ -78,6 +78,7 @@ constexpr int G_SENT = 0x7fffffff;
 struct SplitGemmParams {
   int M, N, K, R, ld, ptr_ld;
   int tiles_m, tiles_n, kb_total, has_tail;
+  int act;               // 0: out [M, N]; 1: SwiGLU over interleaved (gate, up) channel pairs, out [M, N/2]
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
@@ -104,7 +105,7 @@ struct GS {
   static constexpr int DYN = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
 };
 
-template <int BN>
+template <int BN, int ACT>  // ACT 1: SwiGLU over interleaved (gate, up) channel pairs, out [M, N/2]
 __global__ void __launch_bounds__(G_THREADS, 1)
 split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_constant__ CUtensorMap tmap_b4,
                   const __grid_constant__ CUtensorMap tmap_w, const SplitGemmParams p) {
@@ -340,12 +341,19 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
 #pragma unroll
               for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], bs[i]);
             }
-            uint4 o;
-            o.x = f32_to_bf16_bits(d[0]) | (f32_to_bf16_bits(d[1]) << 16);
-            o.y = f32_to_bf16_bits(d[2]) | (f32_to_bf16_bits(d[3]) << 16);
-            o.z = f32_to_bf16_bits(d[4]) | (f32_to_bf16_bits(d[5]) << 16);
-            o.w = f32_to_bf16_bits(d[6]) | (f32_to_bf16_bits(d[7]) << 16);
-            *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+            if (ACT) {
+              uint2 o;
+              o.x = swiglu_bf16_bits(d[0], d[1]) | (swiglu_bf16_bits(d[2], d[3]) << 16);
+              o.y = swiglu_bf16_bits(d[4], d[5]) | (swiglu_bf16_bits(d[6], d[7]) << 16);
+              *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.N + n) / 2) = o;
+            } else {
+              uint4 o;
+              o.x = f32_to_bf16_bits(d[0]) | (f32_to_bf16_bits(d[1]) << 16);
+              o.y = f32_to_bf16_bits(d[2]) | (f32_to_bf16_bits(d[3]) << 16);
+              o.z = f32_to_bf16_bits(d[4]) | (f32_to_bf16_bits(d[5]) << 16);
+              o.w = f32_to_bf16_bits(d[6]) | (f32_to_bf16_bits(d[7]) << 16);
+              *reinterpret_cast<uint4*>(p.out + rowoff + n) = o;
+            }
             if (p.dbg_acc) {
               *reinterpret_cast<int4*>(p.dbg_acc + rowoff + n) =
                   make_int4((int)ri[8 * j] >> 4, (int)ri[8 * j + 1] >> 4, (int)ri[8 * j + 2] >> 4, (int)ri[8 * j + 3] >> 4);
@@ -382,7 +390,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
         // records / counts of this thread's 64-wide half of every K slice of the tile
         const uint32_t* recb = p.rec + ((size_t)mt * 2 * p.kb_total + half) * C * 128 + brow;
         const uint16_t* cntb = p.cnt + ((size_t)mt * 2 * p.kb_total + half) * 128 + brow;
-        auto load_cnt = [&](int kb) -> int {
+        auto load_cnt = [&](int kb) -> int {  // (rows at or beyond M of a partial last tile have zero counts)
           uint32_t n16 = 0u;
           if (kb < p.kb_total) asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(cntb + (size_t)kb * 256));
           return (int)n16;
@@ -473,10 +481,10 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
   }
 }
 
-template <int BN>
+template <int BN, int ACT>
 int launch_split_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot, SplitGemmParams p, cudaStream_t st) {
   using S = GS<BN>;
-  auto kern = split_gemm_kernel<BN>;
+  auto kern = split_gemm_kernel<BN, ACT>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -523,7 +531,7 @@ static int g_gemm_pair_mode = [] {
 int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
                   const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
                   const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
-                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K,
+                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, int act,
                   cudaStream_t st);
 }
 
@@ -557,13 +565,13 @@ extern "C" int tq_set_gemm_pair_mode(int mode) {
   return TQ_OK;
 }
 
-extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
-                                 const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
-                                 const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
-                                 const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
-                                 void* out_bf16,
-                                 int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream) {
-  using namespace tq;
+namespace tq {
+static int run_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
+                              const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
+                              const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
+                              const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
+                              void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, int act,
+                              void* stream) {
   if (!a_q8 || !body_scale || !b_col || !w_scale || !out_bf16 || M < 0 || N <= 0 || K <= 0 || R < 0 || R >= K)
     return TQ_ERR_BAD_ARG;
   if (R > 0 && (!w_rot || !tail_idx16 || !tail_val || tail_ld < R || !tail_ptr || ptr_ld < K / G_BK + 1 || !tail_rec ||
@@ -585,9 +593,10 @@ extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, co
     const bool pair = g_gemm_pair_mode == 1 || (g_gemm_pair_mode < 0 && (R == 0 || tiles_single > 74));
     if (pair)
       return run_pair_gemm(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld,
-                           tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, (cudaStream_t)stream);
+                           tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, act, (cudaStream_t)stream);
   }
   SplitGemmParams p = {};
+  p.act = act;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -607,6 +616,28 @@ extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, co
   p.dbg_acc = dbg_acc;
   p.dbg_tail = dbg_tail;
   const long tiles256 = (long)((M + G_BM - 1) / G_BM) * ((N + 255) / 256);
-  if (tiles256 >= 148) return launch_split_gemm<256>(a_q8, b_col, w_rot, p, (cudaStream_t)stream);
-  return launch_split_gemm<128>(a_q8, b_col, w_rot, p, (cudaStream_t)stream);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tiles256 >= 148)
+    return act ? launch_split_gemm<256, 1>(a_q8, b_col, w_rot, p, st) : launch_split_gemm<256, 0>(a_q8, b_col, w_rot, p, st);
+  return act ? launch_split_gemm<128, 1>(a_q8, b_col, w_rot, p, st) : launch_split_gemm<128, 0>(a_q8, b_col, w_rot, p, st);
+}
+}  // namespace tq
+
+extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
+                                 const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
+                                 const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
+                                 const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
+                                 void* out_bf16,
+                                 int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream) {
+  return tq::run_split_gemm_mma(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr,
+                                ptr_ld, tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, 0, stream);
+}
+
+extern "C" int tq_split_gemm_mma_swiglu(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
+                                        const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
+                                        const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
+                                        const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
+                                        void* out_bf16, int M, int N, int K, void* stream) {
+  return tq::run_split_gemm_mma(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr,
+                                ptr_ld, tail_rec, tail_cnt, R, bias, out_bf16, nullptr, nullptr, M, N, K, 1, stream);
 }

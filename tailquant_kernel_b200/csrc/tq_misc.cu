@@ -52,20 +52,28 @@ __global__ void dequant_finish_kernel(const int32_t* __restrict__ C, const float
   out[i] = (uint16_t)f32_to_bf16_bits(d);
 }
 
-// the same with the accumulators still split over `splits` K ranges ([splits, M, N]): summed here, exactly
+// the same with the accumulators still split over `splits` K ranges ([splits, M, N]): summed here, exactly.
+// act = 1: SwiGLU over interleaved (gate, up) channel pairs, out [M, N/2]; one thread per output either way.
 __global__ void dequant_finish_partials_kernel(const int32_t* __restrict__ P, int splits, const float* __restrict__ sx,
                                                const float* __restrict__ sw, const float* __restrict__ tail,
-                                               const float* __restrict__ bias, uint16_t* __restrict__ out, int M, int N) {
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+                                               const float* __restrict__ bias, uint16_t* __restrict__ out, int M, int N,
+                                               int act) {
+  const size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)M * N;
-  if (i >= total) return;
-  const int m = (int)(i / N), n = (int)(i % N);
-  int acc = 0;
-  for (int s = 0; s < splits; ++s) acc += P[(size_t)s * total + i];
-  float d = __fmul_rn(__fmul_rn((float)acc, sx[m]), sw[n]);
-  if (tail) d = __fadd_rn(d, tail[i]);
-  if (bias) d = __fadd_rn(d, bias[n]);
-  out[i] = (uint16_t)f32_to_bf16_bits(d);
+  const int per = act ? 2 : 1;  // accumulators per output
+  if (o * per >= total) return;
+  float d[2];
+  for (int e = 0; e < per; ++e) {
+    const size_t i = o * per + e;
+    const int m = (int)(i / N), n = (int)(i % N);
+    int acc = 0;
+    for (int s = 0; s < splits; ++s) acc += P[(size_t)s * total + i];
+    float v = __fmul_rn(__fmul_rn((float)acc, sx[m]), sw[n]);
+    if (tail) v = __fadd_rn(v, tail[i]);
+    if (bias) v = __fadd_rn(v, bias[n]);
+    d[e] = v;
+  }
+  out[o] = (uint16_t)(act ? swiglu_bf16_bits(d[0], d[1]) : f32_to_bf16_bits(d[0]));
 }
 
 // ------------------------------------------------------------------ T4 sparse term
@@ -177,12 +185,14 @@ extern "C" int tq_dequant_finish(const int32_t* C, const float* body_scale, cons
 
 extern "C" int tq_dequant_finish_partials(const int32_t* partials, int splits, const float* body_scale,
                                           const float* w_scale, const float* tail, const float* bias, void* out_bf16,
-                                          int M, int N, void* stream) {
-  if (!partials || splits < 1 || !body_scale || !w_scale || !out_bf16 || M < 0 || N <= 0) return TQ_ERR_BAD_ARG;
+                                          int M, int N, int act, void* stream) {
+  if (!partials || splits < 1 || !body_scale || !w_scale || !out_bf16 || M < 0 || N <= 0 || act < 0 || act > 1)
+    return TQ_ERR_BAD_ARG;
+  if (act && (N & 1)) return TQ_ERR_UNSUPPORTED;
   if (M == 0) return TQ_OK;
-  const size_t total = (size_t)M * N;
-  tq::dequant_finish_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      partials, splits, body_scale, w_scale, tail, bias, reinterpret_cast<uint16_t*>(out_bf16), M, N);
+  const size_t outputs = (size_t)M * N / (act ? 2 : 1);
+  tq::dequant_finish_partials_kernel<<<(unsigned)((outputs + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      partials, splits, body_scale, w_scale, tail, bias, reinterpret_cast<uint16_t*>(out_bf16), M, N, act);
   return tq::check_launch();
 }
 

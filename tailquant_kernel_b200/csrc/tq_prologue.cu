@@ -43,8 +43,8 @@ struct PrologueParams {
   uint16_t* tail_idx16;
   uint16_t* tail_val;
   uint16_t* tail_ptr;  // [M, ptr_ld]: entries with index < 128 * j, j = 0 .. K/128
-  uint32_t* tail_rec;  // [ceil(M/128)][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16
-  uint16_t* tail_cnt;  // [ceil(M/128)][K/64][128]: entries per 64-wide half slice
+  uint32_t* tail_rec;  // [2 ceil(M/256)][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16
+  uint16_t* tail_cnt;  // [2 ceil(M/256)][K/64][128]: entries per 64-wide half slice
   int32_t* idx32;
   int8_t* top_q;
   uint16_t* x_rot;
@@ -452,6 +452,15 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
         for (int hs = tid; hs < NHS; hs += NT) {
           const int ea = half_start(hs), eb = hs + 1 < NHS ? half_start(hs + 1) : R;
           p.tail_cnt[((size_t)(m >> 7) * NHS + hs) * 128 + (m & 127)] = (uint16_t)(eb - ea);
+        }
+        if (m == p.M - 1) {
+          // the rows that pad M to a multiple of 256 (the CTA-pair GEMM's tile height) have no entries: the GEMM
+          // kernels rely on these zeros instead of checking rows
+          const int first = p.M, last = (p.M + 255) / 256 * 256;
+          for (int i = tid; i < NHS * (last - first); i += NT) {
+            const int hs = i / (last - first), r = first + i % (last - first);
+            p.tail_cnt[((size_t)(r >> 7) * NHS + hs) * 128 + (r & 127)] = 0;
+          }
         }
       }
       // ---- tail entries, ascending index order

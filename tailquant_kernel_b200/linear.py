@@ -29,17 +29,25 @@ def _side_stream(device) -> "torch.cuda.Stream":
     return st
 
 
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[2 I, K] weight of a fused gate_up projection with rows (gate_0, up_0, gate_1, up_1, ...): the layout
+    `SplitLinear(..., epilogue="swiglu")` expects."""
+    if w_gate.shape != w_up.shape or w_gate.dim() != 2:
+        raise RuntimeError("gate and up weights must be [I, K] tensors of the same shape")
+    return torch.stack((w_gate, w_up), dim=1).reshape(2 * w_gate.shape[0], w_gate.shape[1]).contiguous()
+
+
 class _Workspace:
-    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool):
+    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool, n_out: Optional[int] = None):
         ld = (R + 7) // 8 * 8
         q8 = mma and not small  # the fused GEMM takes INT8 codes; the decode GEMV is faster on the packed form
         self.pro = ops.PrologueOut(
             a_pack=None if q8 else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
             a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=device) if (mma and R) else None,
-            tail_rec=torch.empty(((M + 127) // 128, K // 64, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
+            tail_rec=torch.empty((2 * ((M + 255) // 256), K // 64, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
             if (mma and R) else None,
-            tail_cnt=torch.zeros(((M + 127) // 128, K // 64, 128), dtype=torch.int16, device=device)
+            tail_cnt=torch.zeros((2 * ((M + 255) // 256), K // 64, 128), dtype=torch.int16, device=device)
             if (mma and R) else None,
             body_scale=torch.empty(M, dtype=torch.float32, device=device),
             top_scale=torch.empty(M, dtype=torch.float32, device=device),
@@ -48,7 +56,7 @@ class _Workspace:
             R=R)
         self.tail = torch.empty((M, N), dtype=torch.float32, device=device) if (R and not mma) else None
         self.acc = None  # int32 [splits, M, N], decode path only
-        self.out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        self.out = torch.empty((M, N if n_out is None else n_out), dtype=torch.bfloat16, device=device)
         if small and R:
             self.ev_fork, self.ev_join = torch.cuda.Event(), torch.cuda.Event()
 
@@ -58,12 +66,19 @@ class SplitLinear:
 
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, ratio: float = 0.05,
                  activation_percentile: float = 100.0, had_kind: Optional[int] = None, small_m: int = 64,
-                 split_k: int = 0, tail_engine: str = "mma"):
+                 split_k: int = 0, tail_engine: str = "mma", epilogue: str = "none"):
         """tail_engine: "mma" = tail on the tensor cores inside the GEMM kernel (default, fastest at
         ratios of a few percent); "gather" = exact-order fp32 fma chain on the CUDA cores (bit-exact
-        against the CPU oracle, and the engine of the small-M path)."""
+        against the CPU oracle, and the engine of the small-M path).
+        epilogue: "swiglu" = `weight` is a fused gate_up matrix with interleaved rows (`interleave_gate_up`) and the
+        layer returns bf16(bf16(silu(gate)) * up), [.., N/2], without writing the [.., N] intermediate."""
         if tail_engine not in ("mma", "gather"):
             raise RuntimeError("tail_engine must be 'mma' or 'gather'")
+        if epilogue not in ("none", "swiglu"):
+            raise RuntimeError("epilogue must be 'none' or 'swiglu'")
+        if epilogue == "swiglu" and (tail_engine != "mma" or weight.shape[0] % 16):
+            raise RuntimeError("the SwiGLU epilogue needs the 'mma' tail engine and N % 16 == 0")
+        self.epilogue = epilogue
         self.tail_engine = tail_engine
         if not weight.is_cuda:
             raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
@@ -87,6 +102,7 @@ class SplitLinear:
         if not w.b_col.is_cuda:
             raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
         self = cls.__new__(cls)
+        self.epilogue = "none"
         self.tail_engine = tail_engine
         self.N, self.K = int(w.N), int(w.K)
         self.ratio = float(ratio)
@@ -128,11 +144,15 @@ class SplitLinear:
     def _use_mma(self, M: int) -> bool:
         return self.tail_engine == "mma" and M > self.small_m
 
+    @property
+    def N_out(self) -> int:
+        return self.N // 2 if self.epilogue == "swiglu" else self.N
+
     def workspace(self, M: int) -> _Workspace:
         ws = self._ws.get(M)
         if ws is None:
             ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M),
-                                          M <= self.small_m)
+                                          M <= self.small_m, self.N_out)
         return ws
 
     def _pick_split_k(self, M: int) -> int:
@@ -156,7 +176,7 @@ class SplitLinear:
         w, pro = self.w, ws.pro
         if self._use_mma(M):
             return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot, pro=pro,
-                                      R=self.R, bias=w.bias)
+                                      R=self.R, bias=w.bias, act=self.epilogue)
         if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
             if ws.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
                 splits = ops.gemv_plan(M, self.N, self.K)
@@ -175,7 +195,8 @@ class SplitLinear:
                 cur.wait_event(ws.ev_join)
             else:
                 ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
-            ops.dequant_finish_partials(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
+            ops.dequant_finish_partials(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias,
+                                        act=self.epilogue)
             return ws.out
         if self.R:
             ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
@@ -191,7 +212,7 @@ class SplitLinear:
         M = x2d.shape[0]
         ws = self.prologue(x2d)
         y = self.compute(ws, M)
-        return y.view(*lead, self.N)
+        return y.view(*lead, self.N_out)
 
     __call__ = forward
 

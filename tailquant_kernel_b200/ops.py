@@ -104,8 +104,8 @@ class PrologueOut:
     x_rot: Optional[torch.Tensor] = None  # [M, K] bf16
     a_q8: Optional[torch.Tensor] = None   # [M, K] i8, operand order of split_gemm_mma
     tail_ptr: Optional[torch.Tensor] = None  # [M, K/128 + 1] int16 storage of u16 run boundaries
-    tail_rec: Optional[torch.Tensor] = None  # [ceil(M/128), K/64, 16, 128] int32: tile position | bf16 << 16
-    tail_cnt: Optional[torch.Tensor] = None  # [ceil(M/128), K/64, 128] int16: entries per (row, 64-wide half slice)
+    tail_rec: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 16, 128] int32: tile position | bf16 << 16
+    tail_cnt: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 128] int16: entries per (row, 64-wide half slice)
 
 
 def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
@@ -129,9 +129,9 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
             R=R,
             a_q8=torch.empty((M, K), dtype=torch.int8, device=dev) if want_q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=dev) if (want_q8 and R) else None,
-            tail_rec=torch.empty(((M + 127) // 128, K // 64, TAIL_REC_CAP, 128), dtype=torch.int32, device=dev)
+            tail_rec=torch.empty((2 * ((M + 255) // 256), K // 64, TAIL_REC_CAP, 128), dtype=torch.int32, device=dev)
             if (want_q8 and R) else None,
-            tail_cnt=torch.zeros(((M + 127) // 128, K // 64, 128), dtype=torch.int16, device=dev)
+            tail_cnt=torch.zeros((2 * ((M + 255) // 256), K // 64, 128), dtype=torch.int16, device=dev)
             if (want_q8 and R) else None,
             idx32=torch.empty((M, R), dtype=torch.int32, device=dev) if (t4 and R) else None,
             top_q=torch.empty((M, R), dtype=torch.int8, device=dev) if (t4 and R) else None,
@@ -269,9 +269,11 @@ def split_gemm_fused(A_pack, body_scale, B_pack, w_scale, out, tail=None, bias=N
 
 
 def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Optional[PrologueOut] = None,
-                   R: int = 0, bias=None, dbg_acc=None, dbg_tail=None):
+                   R: int = 0, bias=None, dbg_acc=None, dbg_tail=None, act: str = "none"):
     """One kernel: dense INT4 x INT4 part on tcgen05 kind::i8 plus the tail as a bf16 tensor-core product
-    over the zero-filled tail matrix, fused dequant + bias, bf16 out."""
+    over the zero-filled tail matrix, fused dequant + bias, bf16 out.  act="swiglu": the weight rows are
+    interleaved (gate_i, up_i) pairs and out is [M, N/2] = bf16(bf16(silu(gate)) * up)."""
+    _check(act in ("none", "swiglu"), "act must be 'none' or 'swiglu'")
     _check_cuda(a_q8, "a_q8", torch.int8)
     _check_cuda(B_pack, "B_pack", torch.uint8)
     _check_cuda(body_scale, "body_scale", torch.float32)
@@ -280,7 +282,8 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
     M, K = a_q8.shape
     N = B_pack.shape[0]
     _check(B_pack.shape[1] * 2 == K, "a_q8 and B_pack disagree on K")
-    _check(out.numel() >= M * N, "out too small")
+    _check(out.numel() >= (M * N // 2 if act == "swiglu" else M * N), "out too small")
+    _check(act == "none" or (dbg_acc is None and dbg_tail is None), "no debug outputs with a fused activation")
     ld = 0
     if R:
         _check_cuda(w_rot, "w_rot", torch.bfloat16)
@@ -293,18 +296,21 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
         _check_cuda(tail_rec, "tail_rec", torch.int32)
         _check_cuda(tail_cnt, "tail_cnt", torch.int16)
         _check(tail_ptr.shape[0] == M and tail_ptr.shape[1] >= K // 128 + 1, "tail_ptr must be [M, K/128 + 1]")
-        _check(tuple(tail_rec.shape) == ((M + 127) // 128, K // 64, TAIL_REC_CAP, 128), "tail_rec has the wrong shape")
-        _check(tuple(tail_cnt.shape) == ((M + 127) // 128, K // 64, 128), "tail_cnt has the wrong shape")
+        _check(tuple(tail_rec.shape) == (2 * ((M + 255) // 256), K // 64, TAIL_REC_CAP, 128), "tail_rec has the wrong shape")
+        _check(tuple(tail_cnt.shape) == (2 * ((M + 255) // 256), K // 64, 128), "tail_cnt has the wrong shape")
         ld = tail_idx.shape[1]
     if bias is not None:
         _check_cuda(bias, "bias", torch.float32)
-    rc = _lib.load().tq_split_gemm_mma(_ptr(a_q8), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale),
-                                       _ptr(w_rot) if R else None, _ptr(tail_idx) if R else None,
-                                       _ptr(tail_val) if R else None, ld, _ptr(tail_ptr) if R else None,
-                                       tail_ptr.shape[1] if R else 0, _ptr(tail_rec) if R else None,
-                                       _ptr(tail_cnt) if R else None, int(R), _ptr(bias), _ptr(out),
-                                       _ptr(dbg_acc), _ptr(dbg_tail), M, N, K, _stream())
-    _lib.check(rc, f"split_gemm_mma(M={M}, N={N}, K={K}, R={R})")
+    common = (_ptr(a_q8), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale),
+              _ptr(w_rot) if R else None, _ptr(tail_idx) if R else None,
+              _ptr(tail_val) if R else None, ld, _ptr(tail_ptr) if R else None,
+              tail_ptr.shape[1] if R else 0, _ptr(tail_rec) if R else None,
+              _ptr(tail_cnt) if R else None, int(R), _ptr(bias), _ptr(out))
+    if act == "swiglu":
+        rc = _lib.load().tq_split_gemm_mma_swiglu(*common, M, N, K, _stream())
+    else:
+        rc = _lib.load().tq_split_gemm_mma(*common, _ptr(dbg_acc), _ptr(dbg_tail), M, N, K, _stream())
+    _lib.check(rc, f"split_gemm_mma(M={M}, N={N}, K={K}, R={R}, act={act})")
     return out
 
 
@@ -365,15 +371,17 @@ def gemv_partials(A, B_pack, partials: torch.Tensor) -> torch.Tensor:
     return partials
 
 
-def dequant_finish_partials(partials, body_scale, w_scale, out, tail=None, bias=None):
-    """out = bf16((float(sum_s partials[s]) * body_scale[m]) * w_scale[n] + tail + bias)."""
+def dequant_finish_partials(partials, body_scale, w_scale, out, tail=None, bias=None, act: str = "none"):
+    """out = bf16((float(sum_s partials[s]) * body_scale[m]) * w_scale[n] + tail + bias); act="swiglu" as in
+    split_gemm_mma (out [M, N/2])."""
+    _check(act in ("none", "swiglu"), "act must be 'none' or 'swiglu'")
     _check_cuda(partials, "partials", torch.int32)
     _check(partials.dim() == 3, "partials must be [splits, M, N]")
     S, M, N = partials.shape
     _check_cuda(out, "out", torch.bfloat16)
-    _check(out.numel() >= M * N, "out too small")
+    _check(out.numel() >= (M * N // 2 if act == "swiglu" else M * N), "out too small")
     rc = _lib.load().tq_dequant_finish_partials(_ptr(partials), int(S), _ptr(body_scale), _ptr(w_scale), _ptr(tail),
-                                                _ptr(bias), _ptr(out), M, N, _stream())
+                                                _ptr(bias), _ptr(out), M, N, 1 if act == "swiglu" else 0, _stream())
     _lib.check(rc, f"dequant_finish_partials(S={S}, M={M}, N={N})")
     return out
 

@@ -283,7 +283,7 @@ def tail_records(idx, val_bits, K, cap=16):
     """The regrouped tail lists the fused GEMM reads: run boundaries per 128-wide slice, records and counts per
     64-wide half slice."""
     M, R = idx.shape
-    KB, KH, TM = K // 128, K // 64, (M + 127) // 128
+    KB, KH, TM = K // 128, K // 64, 2 * ((M + 255) // 256)
     ptr = np.stack([np.searchsorted(idx[m].astype(np.int64), np.arange(KB + 1, dtype=np.int64) * 128, side="left")
                     for m in range(M)]).astype(np.uint16) if M else np.zeros((0, KB + 1), np.uint16)
     rec = np.zeros((TM, KH, cap, 128), np.uint32)
@@ -609,3 +609,37 @@ def test_gemv_partials_and_finisher(M, N, K):
     assert torch.equal(out_a, out_b)
     with pytest.raises(RuntimeError):  # a slab count the plan does not give
         ops.gemv_partials(A, B, torch.empty((K // 128 + 3, M, N), dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,I,ratio,pair", [(300, 1024, 264, 0.05, 0), (300, 1024, 264, 0.05, 1), (257, 4096, 512, 0.0, 1),
+                                              (8, 4096, 512, 0.05, -1), (40, 1024, 136, 0.05, -1)])
+def test_swiglu_epilogue(M, K, I, ratio, pair):
+    """The fused gate_up layer with the SwiGLU epilogue equals SwiGLU (CPU oracle) applied to the same layer's
+    plain bf16 outputs: the two runs share every kernel up to the epilogue, so only exp() may differ."""
+    from tailquant_kernel_b200 import SplitLinear, interleave_gate_up
+    rng = np.random.default_rng(M + K + I)
+    wg = torch.from_numpy(rng.standard_normal((I, K)).astype(np.float32) * 0.02).to(torch.bfloat16).cuda()
+    wu = torch.from_numpy(rng.standard_normal((I, K)).astype(np.float32) * 0.02).to(torch.bfloat16).cuda()
+    W = interleave_gate_up(wg, wu)
+    assert torch.equal(W[0::2], wg) and torch.equal(W[1::2], wu)
+    bias = torch.from_numpy(rng.standard_normal(2 * I).astype(np.float32)).cuda()
+    x = dev_bf16(O.make_activations(M, K, seed=5, n_outlier=8))
+    ops.set_gemm_pair_mode(pair)
+    try:
+        plain = SplitLinear(W, bias=bias, ratio=ratio)
+        fused = SplitLinear(W, bias=bias, ratio=ratio, epilogue="swiglu")
+        y = host_bits(plain(x))
+        h = fused(x)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_gemm_pair_mode(-1)
+    assert tuple(h.shape) == (M, I)
+    want, got = O.swiglu_bf16(y), host_bits(h)
+    diff = want != got
+    assert diff.mean() < 2e-3, f"{diff.mean():.5f} of the outputs differ"
+    if diff.any():  # one bf16 step at most (exp() of the device against numpy's)
+        a, b = O.bf16_bits_to_f32(want[diff]), O.bf16_bits_to_f32(got[diff])
+        assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-30)
+    with pytest.raises(RuntimeError):
+        SplitLinear(W, ratio=ratio, epilogue="swiglu", tail_engine="gather")
