@@ -89,6 +89,18 @@ int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int desc
                       uint32_t* tail_rec, uint16_t* tail_cnt, int32_t* idx32, int8_t* top_q, void* x_rot,
                       void* stream);
 
+/* The same prologue with an RMSNorm fused in front of the rotation (the reference runs the norm as a separate
+ * PyTorch module before the linear; x is the un-normalised hidden state, gamma the [K] bf16 norm weight):
+ *   x_n[m,k] = bf16( bf16( x[m,k] / sqrt(mean_k(x[m,:]^2) + rms_eps) ) * gamma[k] ),
+ * the squares summed in fp32 in a fixed order (16 consecutive elements per thread, a butterfly over 32 threads,
+ * eight partial sums in order), then everything as in tq_split_prologue on x_n.  No [M,K] normalised tensor is
+ * written.  (T4 outputs idx32 / top_q are not offered here.) */
+int tq_split_prologue_rmsnorm(const void* x, const void* gamma, float rms_eps, int M, int K, int had_kind, int R,
+                              int descending_rank, float eps, uint8_t* a_pack, int8_t* a_q8, float* body_scale,
+                              float* top_scale, uint16_t* tail_idx16, void* tail_val, int tail_ld,
+                              uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt, void* x_rot,
+                              void* stream);
+
 /* Reference-signature select+pack on an already rotated matrix (T4 outputs):
  * fused_topr_pack(A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps)
  *   tools/fused_topr_pack_ext_v55.py:112-121

@@ -367,6 +367,35 @@ def split_linear_t16(x_bits: np.ndarray, w: PreparedWeight, kind: int, R: int,
     return f32_to_bf16_bits(y), y, p, acc
 
 
+def rmsnorm_bf16(x_bits: np.ndarray, gamma_bits: np.ndarray, eps: float = 1e-6, threads: int = 256) -> np.ndarray:
+    """RMSNorm of bf16 rows as a bf16 framework rounds it (x * rsqrt(mean(x^2) + eps) in fp32 -> bf16, times the
+    bf16 weight -> bf16; e.g. transformers' Qwen3RMSNorm), with the fp32 sum of squares taken in the order of the
+    fused prologue kernel: thread t adds the squares of elements [16 w, 16 w + 16) for w = t, t + threads, ... one
+    after the other, a butterfly (xor 16, 8, 4, 2, 1) adds the 32 threads of a warp, and the warp sums are added in
+    order."""
+    M, K = x_bits.shape
+    x = bf16_bits_to_f32(x_bits)
+    chunks = K // 16
+    sq = (x * x).astype(np.float32).reshape(M, chunks, 16)          # exact: squares of bf16 values fit fp32
+    part = np.zeros((M, threads), np.float32)
+    for w0 in range(0, chunks, threads):
+        n = min(threads, chunks - w0)
+        for e in range(16):
+            part[:, :n] = (part[:, :n] + sq[:, w0:w0 + n, e]).astype(np.float32)
+    lanes = part.reshape(M, threads // 32, 32)
+    idx = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        lanes = (lanes + lanes[:, :, idx ^ o]).astype(np.float32)
+    warp = lanes[:, :, 0]
+    tot = warp[:, 0].copy()
+    for w in range(1, threads // 32):
+        tot = (tot + warp[:, w]).astype(np.float32)
+    mean = (tot / np.float32(K)).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt((mean + np.float32(eps)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    xn = bf16_bits_to_f32(f32_to_bf16_bits((x * inv[:, None]).astype(np.float32)))
+    return f32_to_bf16_bits((xn * bf16_bits_to_f32(gamma_bits)[None, :]).astype(np.float32))
+
+
 def swiglu_bf16(y_bits: np.ndarray) -> np.ndarray:
     """SwiGLU over interleaved (gate, up) columns of a bf16 matrix [M, 2I] -> bf16 bits [M, I], evaluated the way
     a bf16 framework does on the two linears' outputs (the reference computes act(gate) * up in PyTorch,

@@ -51,7 +51,7 @@ extern "C" int tq_prepare_weight(const void* w, int N, int K, int had_kind, floa
   if ((b_row || w_t) && (N % 2 != 0)) return TQ_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   int rc = tq::run_prologue(w, N, K, had_kind, 0, 1, eps, 1, b_col, nullptr, w_scale, nullptr, nullptr, nullptr, 0, nullptr, 0, nullptr, nullptr,
-                            nullptr, nullptr, w_rot, st);
+                            nullptr, nullptr, w_rot, nullptr, 0.0f, st);
   if (rc != TQ_OK) return rc;
   if (w_t) {
     rc = tq::run_transpose_bf16(w_rot, w_t, N, K, st);

@@ -48,6 +48,8 @@ struct PrologueParams {
   int32_t* idx32;
   int8_t* top_q;
   uint16_t* x_rot;
+  const uint16_t* gamma;  // [K] bf16 RMSNorm weight, or NULL: x is used as it is
+  float rms_eps;
 };
 
 // fp32 word index -> physical word index of the row buffer.  Chosen so that the 128-bit
@@ -223,7 +225,7 @@ __device__ __forceinline__ float make_scale(float t, float eps, int mode) {
 // resident CTAs per SM the register budget is tuned for
 constexpr int min_ctas(int K) { return K <= 4096 ? 4 : 2; }
 
-template <int KIND, int K>
+template <int KIND, int K, bool NORM>  // NORM: RMSNorm in front of the rotation (p.gamma, p.rms_eps)
 __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const PrologueParams p) {
   constexpr bool BLOCK = (KIND == TQ_HAD_BLOCK128);
   constexpr int SWB = BLOCK ? 7 : 8;
@@ -261,6 +263,36 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
 
   for (int m = blockIdx.x; m < p.M; m += gridDim.x) {
     const __nv_bfloat16* xrow = p.x + (size_t)m * K;
+    // ---- optional RMSNorm in front of the rotation: inv = 1 / sqrt(mean(x^2) + eps) with the squares summed per
+    // thread in index order (16 contiguous elements, then the thread's next chunks), a butterfly over the warp
+    // and the eight warp sums added in order -- the order the CPU oracle states
+    float rms_inv = 0.0f;
+    if (NORM) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int w0 = 0; w0 < K / 16; w0 += NT) {
+        const int w = w0 + tid;
+        if ((K / 16) % NT == 0 || w < K / 16) {
+          const uint4* src = reinterpret_cast<const uint4*>(xrow + 16 * w);
+          uint4 a = ldg_nc_128(src), b = ldg_nc_128(src + 1);
+          float v[16];
+          unpack8(a, v);
+          unpack8(b, v + 8);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) ss = __fadd_rn(ss, __fmul_rn(v[e], v[e]));
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(FULL, ss, o));
+      float* redf = reinterpret_cast<float*>(red);
+      if (lane == 0) redf[warp] = ss;
+      __syncthreads();
+      float tot = redf[0];
+#pragma unroll
+      for (int w = 1; w < NT / 32; ++w) tot = __fadd_rn(tot, redf[w]);
+      __syncthreads();
+      rms_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.rms_eps)));
+    }
     // ---- pass 1: strides 1,2,4,8 on 16 contiguous elements straight from global memory
 #pragma unroll
     for (int w0 = 0; w0 < K / 16; w0 += NT) {
@@ -271,6 +303,18 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
         float v[16];
         unpack8(a, v);
         unpack8(b, v + 8);
+        if (NORM) {  // y = bf16(bf16(x * inv) * gamma), as a bf16 framework's RMSNorm rounds
+          const uint4 ga = *reinterpret_cast<const uint4*>(p.gamma + 16 * w);
+          const uint4 gb = *reinterpret_cast<const uint4*>(p.gamma + 16 * w + 8);
+          float gm[16];
+          unpack8(ga, gm);
+          unpack8(gb, gm + 8);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float xn = bf16_bits_to_f32(f32_to_bf16_bits(__fmul_rn(v[e], rms_inv)));
+            v[e] = bf16_bits_to_f32(f32_to_bf16_bits(__fmul_rn(xn, gm[e])));
+          }
+        }
         if (KIND != TQ_HAD_NONE) butterflies<16>(v);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -534,9 +578,9 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
   }
 }
 
-template <int KIND, int K>
+template <int KIND, int K, bool NORM>
 int launch(const PrologueParams& p, cudaStream_t st) {
-  auto kern = prologue_kernel<KIND, K>;
+  auto kern = prologue_kernel<KIND, K, NORM>;
   const int Rpad = (p.R + 7) & ~7;
   const size_t smem = (size_t)K * 6 + (128 + 32 + 8 + 64 + 64 + ((K / 64 + 4) & ~3)) * 4 + (size_t)Rpad * 5 + 16;
   static bool configured[64] = {};
@@ -563,7 +607,7 @@ int launch(const PrologueParams& p, cudaStream_t st) {
 }
 
 #define TQ_CASE(KIND, KK) \
-  if (kind == KIND && K == KK) return launch<KIND, KK>(p, st);
+  if (kind == KIND && K == KK) return p.gamma ? launch<KIND, KK, true>(p, st) : launch<KIND, KK, false>(p, st);
 
 int dispatch(int kind, int K, const PrologueParams& p, cudaStream_t st) {
   TQ_CASE(TQ_HAD_WHT, 512)
@@ -598,8 +642,9 @@ float had_scale(int kind, int K) {
 int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float eps, int scale_mode,
                  uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale, uint16_t* tail_idx16,
                  void* tail_val, int tail_ld, uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt,
-                 int32_t* idx32, int8_t* top_q, void* x_rot, cudaStream_t st) {
+                 int32_t* idx32, int8_t* top_q, void* x_rot, const void* gamma, float rms_eps, cudaStream_t st) {
   if ((tail_idx16 || tail_val) && tail_ld < R) return TQ_ERR_BAD_ARG;
+  if (gamma && !aligned16(gamma)) return TQ_ERR_MISALIGNED;
   if (tail_ptr && (ptr_ld < K / 128 + 1 || K % 128 != 0)) return TQ_ERR_BAD_ARG;
   if ((tail_rec != nullptr) != (tail_cnt != nullptr) || (tail_rec && K % 128 != 0)) return TQ_ERR_BAD_ARG;
   if (!x || (!a_pack && !a_q8) || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
@@ -629,6 +674,8 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
   p.idx32 = idx32;
   p.top_q = top_q;
   p.x_rot = reinterpret_cast<uint16_t*>(x_rot);
+  p.gamma = reinterpret_cast<const uint16_t*>(gamma);
+  p.rms_eps = rms_eps;
   return dispatch(had_kind, K, p, st);
 }
 
@@ -641,7 +688,18 @@ extern "C" int tq_split_prologue(const void* x, int M, int K, int had_kind, int 
                                  void* x_rot, void* stream) {
   return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, a_q8, body_scale, top_scale,
                           tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld, tail_rec, tail_cnt, idx32, top_q, x_rot,
-                          (cudaStream_t)stream);
+                          nullptr, 0.0f, (cudaStream_t)stream);
+}
+
+extern "C" int tq_split_prologue_rmsnorm(const void* x, const void* gamma, float rms_eps, int M, int K, int had_kind,
+                                         int R, int descending_rank, float eps, uint8_t* a_pack, int8_t* a_q8,
+                                         float* body_scale, float* top_scale, uint16_t* tail_idx16, void* tail_val,
+                                         int tail_ld, uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec,
+                                         uint16_t* tail_cnt, void* x_rot, void* stream) {
+  if (!gamma) return TQ_ERR_BAD_ARG;
+  return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, a_q8, body_scale, top_scale,
+                          tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld, tail_rec, tail_cnt, nullptr, nullptr, x_rot,
+                          gamma, rms_eps, (cudaStream_t)stream);
 }
 
 extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int descending_rank,
@@ -650,5 +708,6 @@ extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int d
   if (dtype != TQ_BF16) return TQ_ERR_UNSUPPORTED;
   if (R > 0 && (!top_q || !idx || !top_scale)) return TQ_ERR_BAD_ARG;
   return tq::run_prologue(A, M, K, TQ_HAD_NONE, R, descending_rank, eps, 0, A_pack, nullptr, body_scale, top_scale,
-                          nullptr, nullptr, 0, nullptr, 0, nullptr, nullptr, idx, top_q, nullptr, (cudaStream_t)stream);
+                          nullptr, nullptr, 0, nullptr, 0, nullptr, nullptr, idx, top_q, nullptr, nullptr, 0.0f,
+                          (cudaStream_t)stream);
 }

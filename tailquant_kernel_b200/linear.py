@@ -66,12 +66,15 @@ class SplitLinear:
 
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, ratio: float = 0.05,
                  activation_percentile: float = 100.0, had_kind: Optional[int] = None, small_m: int = 64,
-                 split_k: int = 0, tail_engine: str = "mma", epilogue: str = "none"):
+                 split_k: int = 0, tail_engine: str = "mma", epilogue: str = "none",
+                 rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6):
         """tail_engine: "mma" = tail on the tensor cores inside the GEMM kernel (default, fastest at
         ratios of a few percent); "gather" = exact-order fp32 fma chain on the CUDA cores (bit-exact
         against the CPU oracle, and the engine of the small-M path).
         epilogue: "swiglu" = `weight` is a fused gate_up matrix with interleaved rows (`interleave_gate_up`) and the
-        layer returns bf16(bf16(silu(gate)) * up), [.., N/2], without writing the [.., N] intermediate."""
+        layer returns bf16(bf16(silu(gate)) * up), [.., N/2], without writing the [.., N] intermediate.
+        rms_weight: [K] bf16 weight of an RMSNorm that precedes this linear: the layer then takes the UN-normalised
+        hidden state and applies the norm inside its prologue kernel."""
         if tail_engine not in ("mma", "gather"):
             raise RuntimeError("tail_engine must be 'mma' or 'gather'")
         if epilogue not in ("none", "swiglu"):
@@ -79,6 +82,8 @@ class SplitLinear:
         if epilogue == "swiglu" and (tail_engine != "mma" or weight.shape[0] % 16):
             raise RuntimeError("the SwiGLU epilogue needs the 'mma' tail engine and N % 16 == 0")
         self.epilogue = epilogue
+        self.rms_weight = None if rms_weight is None else rms_weight.detach().to(torch.bfloat16).contiguous()
+        self.rms_eps = float(rms_eps)
         self.tail_engine = tail_engine
         if not weight.is_cuda:
             raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
@@ -103,6 +108,7 @@ class SplitLinear:
             raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
         self = cls.__new__(cls)
         self.epilogue = "none"
+        self.rms_weight, self.rms_eps = None, 1e-6
         self.tail_engine = tail_engine
         self.N, self.K = int(w.N), int(w.K)
         self.ratio = float(ratio)
@@ -165,7 +171,8 @@ class SplitLinear:
 
     def prologue(self, x2d: torch.Tensor) -> _Workspace:
         ws = self.workspace(x2d.shape[0])
-        ops.split_prologue(x2d, self.w.had_kind, self.R, self.descending_rank, out=ws.pro)
+        ops.split_prologue(x2d, self.w.had_kind, self.R, self.descending_rank, out=ws.pro,
+                           rms_weight=self.rms_weight, rms_eps=self.rms_eps)
         return ws
 
     def compute(self, ws: _Workspace, M: int) -> torch.Tensor:

@@ -110,8 +110,10 @@ class PrologueOut:
 
 def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
                    eps: float = EPS, t16: bool = True, t4: bool = False, want_x_rot: bool = False,
-                   want_q8: bool = False, want_pack: bool = True, out: Optional[PrologueOut] = None) -> PrologueOut:
-    """Rotation + per-token INT4 + top-R tail split of x [M,K] bf16 in one kernel."""
+                   want_q8: bool = False, want_pack: bool = True, out: Optional[PrologueOut] = None,
+                   rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6) -> PrologueOut:
+    """Rotation + per-token INT4 + top-R tail split of x [M,K] bf16 in one kernel.  With `rms_weight` ([K] bf16)
+    an RMSNorm is applied to x first, inside the same kernel (no T4 outputs then)."""
     _check_cuda(x, "x", torch.bfloat16)
     _check(x.dim() == 2, "x must be [M, K]")
     M, K = x.shape
@@ -139,6 +141,16 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
         )
     ld = out.tail_idx.shape[1] if out.tail_idx is not None else 0
     pld = out.tail_ptr.shape[1] if out.tail_ptr is not None else 0
+    if rms_weight is not None:
+        _check_cuda(rms_weight, "rms_weight", torch.bfloat16)
+        _check(rms_weight.numel() == K, "rms_weight must have K elements")
+        _check(out.idx32 is None and out.top_q is None, "the fused RMSNorm prologue has no T4 outputs")
+        rc = _lib.load().tq_split_prologue_rmsnorm(
+            _ptr(x), _ptr(rms_weight), float(rms_eps), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack),
+            _ptr(out.a_q8), _ptr(out.body_scale), _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld,
+            _ptr(out.tail_ptr), pld, _ptr(out.tail_rec), _ptr(out.tail_cnt), _ptr(out.x_rot), _stream())
+        _lib.check(rc, f"split_prologue_rmsnorm(M={M}, K={K}, had_kind={had_kind}, R={R})")
+        return out
     rc = _lib.load().tq_split_prologue(
         _ptr(x), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack), _ptr(out.a_q8), _ptr(out.body_scale),
         _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld, _ptr(out.tail_ptr), pld, _ptr(out.tail_rec),

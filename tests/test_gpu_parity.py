@@ -643,3 +643,24 @@ def test_swiglu_epilogue(M, K, I, ratio, pair):
         assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-30)
     with pytest.raises(RuntimeError):
         SplitLinear(W, ratio=ratio, epilogue="swiglu", tail_engine="gather")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,K,M,R", [(O.HAD_WHT, 4096, 37, 205), (O.HAD_KRON12, 12288, 9, 615), (O.HAD_WHT, 512, 130, 0),
+                                        (O.HAD_BLOCK128, 2048, 5, 103)])
+def test_prologue_with_fused_rmsnorm(kind, K, M, R):
+    """RMSNorm inside the prologue kernel: every output equals the plain prologue run on the oracle's normalised
+    rows (bit for bit: same sum order, IEEE sqrt / divide, bf16 roundings)."""
+    rng = np.random.default_rng(K + M)
+    xb = O.f32_to_bf16_bits((rng.standard_normal((M, K)) * rng.uniform(0.2, 30.0, (M, 1))).astype(np.float32))
+    gb = O.f32_to_bf16_bits((1.0 + 0.3 * rng.standard_normal(K)).astype(np.float32))
+    xn = O.rmsnorm_bf16(xb, gb, eps=1e-6)
+    fused = ops.split_prologue(dev_bf16(xb), kind, R, want_q8=True, want_x_rot=True, rms_weight=dev_bf16(gb.reshape(1, -1)).reshape(-1),
+                               rms_eps=1e-6)
+    plain = ops.split_prologue(dev_bf16(xn), kind, R, want_q8=True, want_x_rot=True)
+    torch.cuda.synchronize()
+    ref = O.prologue(xn, kind, R)
+    assert np.array_equal(host_bits(fused.x_rot), ref.x_rot), "rotated normalised activations"
+    for name in ("a_pack", "a_q8", "body_scale", "top_scale", "x_rot") + (("tail_idx", "tail_val", "tail_ptr", "tail_cnt") if R else ()):
+        a, b = getattr(fused, name), getattr(plain, name)
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), name
