@@ -470,6 +470,8 @@ def run_extra(args) -> None:
     """Secondary workloads of the baseline (one JSON line per case, device time by CUDA events):
     decode      : Qwen3-8B layer shapes at M in {1, 8, 32, 64}, split-K path, int4-weight GB/s against HBM peak
     llama_sweep : Llama-3-8B layer shapes at M = 4096, ratios 0 / 0.01 / 0.05 / 0.10 (K = 14336 uses block-128)
+    prefill36   : baseline config 3 (Qwen3-8B, 36 layers, seq 4096, random init): whole-prefill latency with all linears on
+                  the split path and bf16 attention
     single      : baseline config 1 (M = 512, K = N = 4096, ratio 0.05), both tail engines
     latency_table : CSV `K,N,ratio,b16,b64,b256` (ms per forward at 16 / 64 / 256 token rows, CUDA-graph replay) in
                   the format the reference's policy calibrator reads
@@ -560,6 +562,95 @@ def run_extra(args) -> None:
                     cols.append(graph_ms_of(lambda: lin.forward(x)))
                 print(f"{K},{N},{ratio},{cols[0]:.5f},{cols[1]:.5f},{cols[2]:.5f}", flush=True)
                 del lin
+    elif args.workload == "prefill36":
+        # Baseline config 3: Qwen3-8B, 36 decoder layers, random init, batch 1 x seq 4096, every linear of a layer on the
+        # split W4A4 + tail path at ratio 0.05 (qkv and gate_up as fused projections, input / post-attention RMSNorm
+        # folded into their prologues, SwiGLU folded into the gate_up epilogue), attention in bf16 (torch SDPA).
+        # Compared with the same stack on bf16 cuBLAS linears.  Whole-prefill latency, CUDA events.
+        import torch.nn.functional as F
+        from tailquant_kernel_b200 import interleave_gate_up
+        H, NH, NKV, HD, I, L, S = 4096, 32, 8, 128, 12288, args.layers, args.seq_len
+        theta, rms_eps = 1e6, 1e-6
+        g = torch.Generator(device="cpu")
+        g.manual_seed(5)
+
+        def rnd(n, k):
+            return (torch.randn((n, k), generator=g) * 0.02).to(torch.bfloat16).to(dev)
+
+        def rms(x, w):
+            v = x.float()
+            return (w * (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + rms_eps)).to(torch.bfloat16))
+
+        pos = torch.arange(S, device=dev, dtype=torch.float32)
+        inv = 1.0 / (theta ** (torch.arange(0, HD, 2, device=dev, dtype=torch.float32) / HD))
+        ang = pos[:, None] * inv[None, :]
+        cos, sin = torch.cat((ang.cos(), ang.cos()), -1).to(torch.bfloat16), torch.cat((ang.sin(), ang.sin()), -1).to(torch.bfloat16)
+
+        def rope(t):  # t [S, heads, HD]
+            t1, t2 = t[..., : HD // 2], t[..., HD // 2:]
+            return t * cos[:, None, :] + torch.cat((-t2, t1), -1) * sin[:, None, :]
+
+        layers = []
+        for li in range(L):
+            wq, wk, wv, wo = rnd(NH * HD, H), rnd(NKV * HD, H), rnd(NKV * HD, H), rnd(H, NH * HD)
+            wg, wu, wd = rnd(I, H), rnd(I, H), rnd(H, I)
+            ones = torch.ones(H, dtype=torch.bfloat16, device=dev)
+            qn, kn = torch.ones(HD, dtype=torch.bfloat16, device=dev), torch.ones(HD, dtype=torch.bfloat16, device=dev)
+            wqkv = torch.cat((wq, wk, wv), 0)
+            lay = {"ln1": ones, "ln2": ones.clone(), "qn": qn, "kn": kn,
+                   "s_qkv": SplitLinear(wqkv, ratio=RATIO, rms_weight=ones, rms_eps=rms_eps),
+                   "s_o": SplitLinear(wo, ratio=RATIO),
+                   "s_gu": SplitLinear(interleave_gate_up(wg, wu), ratio=RATIO, rms_weight=ones, rms_eps=rms_eps, epilogue="swiglu"),
+                   "s_d": SplitLinear(wd, ratio=RATIO, had_kind=None)}
+            if args.with_bf16:
+                lay.update({"wqkv": wqkv, "wo": wo, "wgu": torch.cat((wg, wu), 0), "wd": wd})
+            layers.append(lay)
+            del wq, wk, wv, wg, wu
+        x0 = (torch.randn((S, H), generator=g) * 1.0).to(torch.bfloat16).to(dev)
+
+        def attention(qkv, lay):
+            q, k, v = qkv.split((NH * HD, NKV * HD, NKV * HD), -1)
+            q = rope(rms(q.view(S, NH, HD), lay["qn"]))
+            k = rope(rms(k.view(S, NKV, HD), lay["kn"]))
+            o = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
+                                               v.view(S, NKV, HD).transpose(0, 1)[None], is_causal=True, enable_gqa=True)
+            return o[0].transpose(0, 1).reshape(S, NH * HD)
+
+        def forward_split():
+            h = x0
+            for lay in layers:
+                a = attention(lay["s_qkv"](h), lay)          # input RMSNorm inside the prologue
+                h = h + lay["s_o"](a)
+                h = h + lay["s_d"](lay["s_gu"](h))           # post-attention RMSNorm in the prologue, SwiGLU in the epilogue
+            return h
+
+        def forward_bf16():
+            h = x0
+            for lay in layers:
+                a = attention(F.linear(rms(h, lay["ln1"]), lay["wqkv"]), lay)
+                h = h + F.linear(a, lay["wo"])
+                gu = F.linear(rms(h, lay["ln2"]), lay["wgu"])
+                h = h + F.linear(F.silu(gu[:, :I]) * gu[:, I:], lay["wd"])
+            return h
+
+        t_split = ms_of(forward_split, reps=5)
+        out = {"workload": "prefill36", "layers": L, "seq_len": S, "hidden": H, "ratio": RATIO,
+               "split_prefill_ms": t_split, "tokens_per_s": S / (t_split * 1e-3),
+               "attention": "torch SDPA bf16 (GQA 32/8, head_dim 128, RoPE theta 1e6, q/k RMSNorm)",
+               "fusions": "RMSNorm in the qkv / gate_up prologues, SwiGLU in the gate_up epilogue"}
+        if args.with_bf16:
+            t_bf = ms_of(forward_bf16, reps=5)
+            out.update({"bf16_prefill_ms": t_bf, "split_over_bf16": t_split / t_bf})
+        # time spent outside the linears (attention, RoPE, norms of q/k, residual adds), measured on the same stack
+        def forward_rest():
+            h = x0
+            qkv = torch.empty((S, (NH + 2 * NKV) * HD), dtype=torch.bfloat16, device=dev).normal_()
+            for lay in layers:
+                a = attention(qkv, lay)
+                h = h + a
+            return h
+        out["non_linear_part_ms"] = ms_of(forward_rest, reps=5)
+        print(json.dumps(out), flush=True)
     elif args.workload == "llama_sweep":
         shapes = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
         M = 4096
@@ -596,8 +687,11 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tail-engine", default="mma", choices=["mma", "gather"],
                     help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
-    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single", "latency_table"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single", "latency_table", "prefill36"],
                     help="layer = the benchmark proper (baseline configs[1]); the others print secondary figures")
+    ap.add_argument("--layers", type=int, default=36, help="prefill36: decoder layers")
+    ap.add_argument("--seq-len", type=int, default=4096, help="prefill36: tokens")
+    ap.add_argument("--with-bf16", action="store_true", help="prefill36: also time the same stack on bf16 cuBLAS linears")
     args = ap.parse_args()
     M_TOKENS = args.rows_per_gpu
     METRIC = METRIC.replace("M=2048/GPU", f"M={M_TOKENS}/GPU")

@@ -91,8 +91,10 @@ class SplitLinear:
         self.ratio = float(ratio)
         self.R = ops.ceil_ratio_count(self.K, self.ratio)
         _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
-        self.w = ops.prepare_weight(weight, had_kind, t16=self.R > 0, keep_w_rot=self.R > 0 and tail_engine == "mma",
-                                    bias=bias)
+        # the [K, N] transpose of the rotated weights serves the gather engine and the decode tail; with the
+        # tensor-core tail it is built on the first small-M call only (it doubles the bf16 weight memory)
+        self.w = ops.prepare_weight(weight, had_kind, t16=self.R > 0 and tail_engine == "gather",
+                                    keep_w_rot=self.R > 0 and tail_engine == "mma", bias=bias)
         self.small_m = int(small_m)
         self.split_k = int(split_k)
         self.activation_percentile = float(activation_percentile)
@@ -116,10 +118,9 @@ class SplitLinear:
         _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
         if self.R > 0 and tail_engine == "mma" and w.w_rot is None:
             raise RuntimeError("the tensor-core tail needs the rotated bf16 weights (w_rot)")
-        if self.R > 0 and w.w_t is None and w.w_rot is not None:
-            # the decode path and the gather engine read the [K, N] transpose
-            w.w_t = w.w_rot.t().contiguous()
-        if self.R > 0 and w.w_t is None:
+        if self.R > 0 and tail_engine == "gather" and w.w_t is None and w.w_rot is not None:
+            w.w_t = w.w_rot.t().contiguous()  # the gather engine reads the [K, N] transpose
+        if self.R > 0 and w.w_t is None and w.w_rot is None:
             raise RuntimeError("a tail needs the rotated bf16 weights (w_rot or w_t)")
         self.w = w
         self.small_m = int(small_m)
@@ -188,6 +189,8 @@ class SplitLinear:
             if ws.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
                 splits = ops.gemv_plan(M, self.N, self.K)
                 ws.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=ws.out.device)
+            if self.R and w.w_t is None:
+                w.w_t = w.w_rot.t().contiguous()  # first small-M call of a layer prepared for the tensor-core tail
             if self.R:
                 # the tail sums and the GEMV only depend on the prologue and neither fills the GPU at these sizes:
                 # the tail runs on a side stream next to the GEMV (a parallel branch when captured in a CUDA graph)
