@@ -8,6 +8,8 @@ rounded bf16 output can sit further than 2e-2 from the fp32 value; the tests the
 (a) bit equality with bf16(oracle fp32) and (b) the stated bounds against the fp32 value with the
 max-abs bound applied in units of half an output ulp where that is larger than 2e-2.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -664,3 +666,19 @@ def test_prologue_with_fused_rmsnorm(kind, K, M, R):
     for name in ("a_pack", "a_q8", "body_scale", "top_scale", "x_rot") + (("tail_idx", "tail_val", "tail_ptr", "tail_cnt") if R else ()):
         a, b = getattr(fused, name), getattr(plain, name)
         assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), name
+
+
+@pytest.mark.gpu
+def test_column_parallel_two_gpus():
+    """Optional N-split over two GPUs with one NCCL all-gather (skipped on a one-GPU box)."""
+    import subprocess
+    import sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29571",
+                          os.path.join(here, "column_parallel_worker.py")],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
