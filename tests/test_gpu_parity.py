@@ -49,6 +49,11 @@ def make_x(M, K, seed, kind="outlier"):
         e = rng.integers(-30, 10, size=(M, K)).astype(np.float32)
         v = rng.standard_normal((M, K), dtype=np.float32) * np.exp2(e)
         return O.f32_to_bf16_bits(v)
+    if kind == "col257":  # the reference's own test pattern: N(0,1) with every 257th column x8
+        # (tools/compare_single_matrix_fake_vs_kernel_quant_l2_v1.py:155-157)
+        v = rng.standard_normal((M, K), dtype=np.float32)
+        v[:, ::257] *= np.float32(8.0)
+        return O.f32_to_bf16_bits(v)
     if kind == "zeros":
         v = rng.standard_normal((M, K), dtype=np.float32)
         v[0] = 0.0
@@ -81,6 +86,14 @@ PROLOGUE_CASES = [
     (O.HAD_NONE, 1024, 8, 60, "wide", 97.0),
     (O.HAD_NONE, 12288, 5, 615, "ties", 100.0),
     (O.HAD_NONE, 14336, 5, 144, "outlier", 100.0),
+    # input pattern, R values and percentiles of the reference's own sweeps (tools/bench_topr_select_algos_v38.py:80-83,
+    # tools/smoke_split_kernel_optimization_5points_v1.py:38-39)
+    (O.HAD_NONE, 4096, 16, 41, "col257", 98.3),
+    (O.HAD_NONE, 4096, 16, 82, "col257", 99.477),
+    (O.HAD_NONE, 4096, 16, 164, "col257", 98.3),
+    (O.HAD_WHT, 4096, 12, 21, "col257", 100.0),
+    (O.HAD_WHT, 4096, 12, 30, "col257", 100.0),
+    (O.HAD_KRON12, 12288, 6, 63, "col257", 100.0),
 ]
 
 
