@@ -521,6 +521,8 @@ def run_extra(args) -> None:
 
     if args.workload == "decode":
         for name, K, N in LAYER:
+            if args.only and name != args.only:
+                continue
             _, W = data(1, K, N, 7)
             lin = SplitLinear(W, ratio=RATIO, tail_engine="gather")
             n_copies = max(2, int((300 * 2 ** 20) // (K * N // 2)) + 1)
@@ -689,6 +691,7 @@ def main() -> None:
                     help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
     ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single", "latency_table", "prefill36"],
                     help="layer = the benchmark proper (baseline configs[1]); the others print secondary figures")
+    ap.add_argument("--only", default="", help="decode: restrict to one linear (qkv_proj, o_proj, gate_up_proj, down_proj)")
     ap.add_argument("--layers", type=int, default=36, help="prefill36: decoder layers")
     ap.add_argument("--seq-len", type=int, default=4096, help="prefill36: tokens")
     ap.add_argument("--with-bf16", action="store_true", help="prefill36: also time the same stack on bf16 cuBLAS linears")

@@ -120,9 +120,14 @@ gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b
               const unsigned char* plo = sm_a + (16 * t + g) * pitch + s * DV_KS + j * 32;
               const unsigned char* phi = sm_a + (16 * t + g + 8) * pitch + s * DV_KS + j * 32;
               const uint4 l0 = *reinterpret_cast<const uint4*>(plo), l1 = *reinterpret_cast<const uint4*>(plo + 16);
-              const uint4 h0 = *reinterpret_cast<const uint4*>(phi), h1 = *reinterpret_cast<const uint4*>(phi + 16);
               a[0] = l0.x, a[1] = l0.y, a[2] = l0.z, a[3] = l0.w, a[4] = l1.x, a[5] = l1.y, a[6] = l1.z, a[7] = l1.w;
-              c[0] = h0.x, c[1] = h0.y, c[2] = h0.z, c[3] = h0.w, c[4] = h1.x, c[5] = h1.y, c[6] = h1.z, c[7] = h1.w;
+              if (MT > 1 || hi_rows) {
+                const uint4 h0 = *reinterpret_cast<const uint4*>(phi), h1 = *reinterpret_cast<const uint4*>(phi + 16);
+                c[0] = h0.x, c[1] = h0.y, c[2] = h0.z, c[3] = h0.w, c[4] = h1.x, c[5] = h1.y, c[6] = h1.z, c[7] = h1.w;
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) c[i] = 0u;
+              }
             } else {
               const uint4 alo = *reinterpret_cast<const uint4*>(sm_a + (16 * t + g) * pitch + s * (DV_KS / 2) + j * 16);
               widen16(alo, a);
