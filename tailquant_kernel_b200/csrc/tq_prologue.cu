@@ -540,12 +540,11 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
     for (int j = 0; j < J; ++j) {
       const int g = tid + NT * j;
       if ((GN % NT == 0) || g < GN) {
-        uint32_t packw = 0u, qlo = 0u, qhi = 0u;
+        uint32_t qlo = 0u, qhi = 0u;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const float xv = bf16_bits_to_f32(pk[8 * j + c] >> 16);
+          const float xv = __uint_as_float(pk[8 * j + c] & 0xffff0000u);
           const int code = ((tm[j] >> c) & 1u) ? 0 : quant_s4(xv, bscale, brinv);
-          packw |= ((uint32_t)code & 0xfu) << (4 * c);
           // INT8 form: even elements of the group first, then the odd ones -- the order in which the GEMM's
           // widening of the packed INT4 weights lays out K
           if (c & 1)
@@ -553,6 +552,8 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
           else
             qlo |= ((uint32_t)code & 0xffu) << (8 * (c >> 1));
         }
+        // packed form: nibble c = element c, i.e. the low nibbles of the even bytes interleaved with the odd ones
+        const uint32_t packw = (qlo & 0x0f0f0f0fu) | ((qhi & 0x0f0f0f0fu) << 4);
         if (p.a_pack) *reinterpret_cast<uint32_t*>(p.a_pack + (size_t)m * (K / 2) + 4 * g) = packw;
         if (p.a_q8) *reinterpret_cast<uint2*>(p.a_q8 + (size_t)m * K + 8 * g) = make_uint2(qlo, qhi);
       }
