@@ -92,8 +92,7 @@ __device__ __forceinline__ uint32_t block_max(uint32_t v, uint32_t* red, int tid
   uint32_t r = red[0];
 #pragma unroll
   for (int w = 1; w < NT / 32; ++w) r = max(r, red[w]);
-  __syncthreads();
-  return r;
+  return r;  // red[0..7] stay untouched until the next row: the rank selection uses red[16..31]
 }
 
 struct SelRes {
@@ -109,6 +108,8 @@ __device__ __forceinline__ SelRes select_rank(const uint32_t (&pk)[E], int rank,
                                               uint32_t* hist, int* res, int tid) {
   const int lane = tid & 31, warp = tid >> 5;
   int below = 0, base = 0, dstar = 0, cum_prev = 0;
+  red += 16;                      // (the first half of `red` belongs to block_max)
+  if (tid < 128) hist[tid] = 0;   // ordered before the histogram adds by the barrier(s) of the loop below
   while (true) {  // uniform across the block: every value below comes from shared memory
     uint32_t c = 0;
 #pragma unroll
@@ -130,7 +131,6 @@ __device__ __forceinline__ SelRes select_rank(const uint32_t (&pk)[E], int rank,
       lo += red[w * 2];
       hi += red[w * 2 + 1];
     }
-    __syncthreads();
     int cum[4] = {below + (int)(lo & 0xffffu), below + (int)(hi & 0xffffu), below + (int)(lo >> 16),
                   below + (int)(hi >> 16)};
     bool found = false;
@@ -143,12 +143,11 @@ __device__ __forceinline__ SelRes select_rank(const uint32_t (&pk)[E], int rank,
       }
     }
     if (found || base >= 256) break;
+    __syncthreads();  // every thread has read the counters before the next round overwrites them
     below = cum[3];
     base += 4;
   }
 
-  if (tid < 128) hist[tid] = 0;
-  __syncthreads();
 #pragma unroll
   for (int e = 0; e < E; ++e) {
     uint32_t kp = pk[e] & 0xffffu;
@@ -214,8 +213,7 @@ __device__ __forceinline__ SelRes select_rank(const uint32_t (&pk)[E], int rank,
   out.cnt_eq = res[2];
   int nb = res[3] >= 0 ? res[3] : res[4];
   out.next_kp = nb >= 0 ? dstar * 128 + nb : -1;
-  __syncthreads();
-  return out;
+  return out;  // (a later call rewrites hist / res only behind its own barriers)
 }
 
 __device__ __forceinline__ float make_scale(float t, float eps, int mode) {
@@ -575,7 +573,8 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
         if (p.top_scale) p.top_scale[m] = tscale;
       }
     }
-    __syncthreads();  // the tail staging and the bf16 row are rewritten by the next row
+    // (no barrier here: the next row touches the tail staging, the bf16 row, `red` and `res` only behind several
+    // of its own barriers, which every thread of this row reaches after its copy-out)
   }
 }
 
