@@ -90,7 +90,8 @@ int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int desc
                       void* stream);
 
 /* The same prologue with an RMSNorm fused in front of the rotation (the reference runs the norm as a separate
- * PyTorch module before the linear; x is the un-normalised hidden state, gamma the [K] bf16 norm weight):
+ * PyTorch module before the linear: tools/bench_layer_async_schedule_v22.py:237,249 -- `layer.input_layernorm`,
+ * `layer.post_attention_layernorm`; x is the un-normalised hidden state, gamma the [K] bf16 norm weight):
  *   x_n[m,k] = bf16( bf16( x[m,k] / sqrt(mean_k(x[m,:]^2) + rms_eps) ) * gamma[k] ),
  * the squares summed in fp32 in a fixed order (16 consecutive elements per thread, a butterfly over 32 threads,
  * eight partial sums in order), then everything as in tq_split_prologue on x_n.  No [M,K] normalised tensor is
