@@ -678,7 +678,7 @@ def run_extra(args) -> None:
 
 
 def main() -> None:
-    global M_TOKENS, METRIC
+    global M_TOKENS, METRIC, CPU_SAMPLE_ROWS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--rows-per-gpu", type=int, default=M_TOKENS,
@@ -691,12 +691,15 @@ def main() -> None:
                     help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
     ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single", "latency_table", "prefill36"],
                     help="layer = the benchmark proper (baseline configs[1]); the others print secondary figures")
+    ap.add_argument("--reference-rows", type=int, default=CPU_SAMPLE_ROWS,
+                    help="token rows of the 2048 that the CPU arm (and the cpu_baseline leg) works through per step")
     ap.add_argument("--only", default="", help="decode: restrict to one linear (qkv_proj, o_proj, gate_up_proj, down_proj)")
     ap.add_argument("--layers", type=int, default=36, help="prefill36: decoder layers")
     ap.add_argument("--seq-len", type=int, default=4096, help="prefill36: tokens")
     ap.add_argument("--with-bf16", action="store_true", help="prefill36: also time the same stack on bf16 cuBLAS linears")
     args = ap.parse_args()
     M_TOKENS = args.rows_per_gpu
+    CPU_SAMPLE_ROWS = args.reference_rows
     METRIC = METRIC.replace("M=2048/GPU", f"M={M_TOKENS}/GPU")
     if args.workload != "layer":
         run_extra(args)
