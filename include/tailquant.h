@@ -34,9 +34,9 @@ extern "C" {
 #define TQ_HAD_KRON12 2   /* K = 12*2^n (6144, 12288): (H12 (x) H_2^n)/sqrt(K), H12 = Paley */
 #define TQ_HAD_BLOCK128 3 /* K % 2048 == 0 (e.g. 14336): block-diagonal H128/sqrt(128)      */
 
-/* Entries per (row, 128-wide K slice) held by the tail records; longer runs are completed from the
- * sorted lists. */
-#define TQ_TAIL_REC_CAP 16
+/* Entries per (row, 64-wide half of a K slice) held by the tail records (a record is 48 bytes: three 128-bit
+ * loads); longer runs are completed from the sorted lists. */
+#define TQ_TAIL_REC_CAP 12
 
 /* 16-bit float formats of activation inputs / outputs. */
 #define TQ_BF16 0
@@ -71,11 +71,12 @@ const char* tq_last_cuda_error(void);
  *   tail_ld      row pitch (elements) of tail_idx16 / tail_val, >= R; idx32 / top_q are dense [M,R]
  *   tail_ptr     [M,ptr_ld] u16, ptr_ld >= K/128 + 1: tail_ptr[m][j] = number of tail entries of row m
  *                with index < 128 j (run boundaries for tq_split_gemm_mma; K % 128 == 0; may be NULL)
- *   tail_rec     [2 ceil(M/256)][K/64][TQ_TAIL_REC_CAP][128] u32: the same entries regrouped per 128-row
- *                tile and 64-wide half of a K slice, entry j of the 128 rows contiguous -- what
- *                tq_split_gemm_mma reads, one coalesced load per j.  Entry = bf16 bits << 16 | p, where
- *                p = ((((index & 63) >> 3) ^ (m & 7)) << 3) | (index & 7) is half the byte offset of the
- *                value in its 128-byte row of the 128-byte-swizzled operand tile (may be NULL)
+ *   tail_rec     [2 ceil(M/256)][K/64][128][TQ_TAIL_REC_CAP] u32: the same entries regrouped per 128-row
+ *                tile and 64-wide half of a K slice, one record of TQ_TAIL_REC_CAP consecutive words per row (the
+ *                first min(count, TQ_TAIL_REC_CAP) entries of that half, ascending; the other words are not
+ *                written) -- what tq_split_gemm_mma reads, three 128-bit loads per row and half.  Entry = bf16
+ *                bits << 16 | p, where p = ((((index & 63) >> 3) ^ (m & 7)) << 3) | (index & 7) is half the byte
+ *                offset of the value in its 128-byte row of the 128-byte-swizzled operand tile (may be NULL)
  *   tail_cnt     [2 ceil(M/256)][K/64][128] u16 entries per (row, half slice) (with tail_rec); the rows that
  *                pad M to a multiple of 256 are written as 0 (both arrays cover them: the CTA-pair GEMM
  *                works on 256-row tiles and does not check rows)
@@ -267,9 +268,10 @@ int tq_int4_linear_splitk_noalloc(const uint8_t* a_pack, const float* body_scale
                                   const float* w_scale, const float* tail, const float* bias, void* out_bf16,
                                   int M, int N, int K, int split_k, void* stream);
 
-/* Status word of the last GEMM launches on the current device: 0, or a code naming the
- * pipeline wait that ran out of its iteration budget (the kernel then drains and returns
- * instead of spinning).  Synchronises the device. */
+/* Status word of the GEMM launches on the current device since the previous call: 0, or a code naming the
+ * pipeline wait that ran out of its time budget (the kernel then drains and returns instead of spinning; its
+ * output is not valid).  Synchronises the device, returns TQ_ERR_DEVICE_STATUS when the word is non-zero and
+ * clears it, so poll it at a synchronisation point after the launches whose result matters. */
 int tq_gemm_status(unsigned int* status);
 
 #ifdef __cplusplus

@@ -12,6 +12,12 @@ void set_last_cuda_error(cudaError_t e) {
   g_cuda_error[i] = 0;
 }
 
+void set_last_error_text(const char* s) {
+  int i = 0;
+  for (; s && s[i] && i < 255; ++i) g_cuda_error[i] = s[i];
+  g_cuda_error[i] = 0;
+}
+
 int check_launch() {
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return TQ_OK;

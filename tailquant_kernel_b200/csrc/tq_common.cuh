@@ -12,6 +12,7 @@ namespace tq {
 
 // ---------------------------------------------------------------------------- host side
 void set_last_cuda_error(cudaError_t e);
+void set_last_error_text(const char* s);  // message for failures that have no cudaError_t (driver entry points)
 int check_launch();  // cudaGetLastError -> TQ_OK / TQ_ERR_CUDA
 
 int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float eps, int scale_mode,

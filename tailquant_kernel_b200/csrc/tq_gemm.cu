@@ -414,6 +414,10 @@ extern "C" int tq_gemm_status(unsigned int* status) {
   if (!status) return TQ_ERR_BAD_ARG;
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemcpyFromSymbol(status, tq::g_status, sizeof(unsigned int));
+  if (e == cudaSuccess && *status) {  // read-and-clear: a code reports the launches since the previous call
+    const unsigned int zero = 0;
+    e = cudaMemcpyToSymbol(tq::g_status, &zero, sizeof(unsigned int));
+  }
   if (e != cudaSuccess) {
     tq::set_last_cuda_error(e);
     return TQ_ERR_CUDA;

@@ -37,7 +37,7 @@ struct PairGemmParams {
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
-  const uint32_t* rec;   // [2 tiles_m][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
+  const uint32_t* rec;   // [2 tiles_m][K/64][128][TQ_TAIL_REC_CAP]: tile position | bf16 << 16 (see tq_split_prologue)
   const uint16_t* cnt;   // [2 tiles_m][K/64][128]: entries of the row in the 64-wide half slice (0 for rows >= M)
   const float* sx;
   const float* sw;
@@ -372,8 +372,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
   } else {
     // ------------------------------------------------------------------ tail builders (+ epilogue share)
     // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
-    // bf16 tail tile of that half.  The row's entries of a slice come as one record column
-    // ([slice][j][row]: a warp reads 128 contiguous bytes per j), fetched two slices ahead; the record
+    // bf16 tail tile of that half.  The row's entries of a half slice come as one record of TQ_TAIL_REC_CAP words
+    // ([half slice][row][j]: 128-bit loads, a warp reads one contiguous run), fetched one slice ahead; a word
     // already holds the swizzled position of the value inside the 128-byte tile row.
     if (has_tail) {
       constexpr int C = TQ_TAIL_REC_CAP;
@@ -392,12 +392,15 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       size_t fhs = my_tiles > 0 ? ((size_t)(2 * tile_mt(0) + (int)rank) * kbt) * 2 + half : 0;
       auto fetch = [&](uint32_t(&r)[C], int& n) {
         if (fi < my_tiles) {
-          const uint32_t* recb = p.rec + fhs * C * 128 + brow;
+          const uint4* recb = reinterpret_cast<const uint4*>(p.rec + (fhs * 128 + brow) * C);
           uint32_t n16;
           asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + fhs * 128 + brow));
           n = (int)n16;
 #pragma unroll
-          for (int j = 0; j < C; ++j) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + (size_t)j * 128));
+          for (int j = 0; j < C / 4; ++j)  // the row's record: C words in a row, a warp reads 32 C contiguous words
+            asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r[4 * j]), "=r"(r[4 * j + 1]), "=r"(r[4 * j + 2]), "=r"(r[4 * j + 3])
+                         : "l"(recb + j));
           fhs += 2;
           if (++fkb == kbt) {  // next tile of the pair
             fkb = 0;

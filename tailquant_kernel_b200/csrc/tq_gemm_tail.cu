@@ -82,7 +82,7 @@ struct SplitGemmParams {
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
-  const uint32_t* rec;   // [tiles_m][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16 (see tq_split_prologue)
+  const uint32_t* rec;   // [tiles_m][K/64][128][TQ_TAIL_REC_CAP]: tile position | bf16 << 16 (see tq_split_prologue)
   const uint16_t* cnt;   // [tiles_m][K/64][128]: entries of the row in the 64-wide half slice
   const float* sx;
   const float* sw;
@@ -374,9 +374,9 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
   } else if (warp < 6 + G_BUILD_WARPS) {
     // ------------------------------------------------------------------ tail builders
     // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
-    // bf16 tail tile of that half.  The row's entries of a slice come as one record column
-    // ([slice][j][row]: a warp reads 128 contiguous bytes per j), fetched two slices ahead; the record
-    // already holds the swizzled position of the value inside the 128-byte tile row.
+    // bf16 tail tile of that half.  The row's entries of a half slice come as one record of TQ_TAIL_REC_CAP words
+    // ([half slice][row][j]: 128-bit loads), fetched two slices ahead; a word already holds the swizzled
+    // position of the value inside the 128-byte tile row.
     if (has_tail) {
       constexpr int C = TQ_TAIL_REC_CAP;
       const int btid = threadIdx.x - 6 * 32;
@@ -388,7 +388,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
         const int mt = t % p.tiles_m;
         const int grow = mt * G_BM + brow;
         // records / counts of this thread's 64-wide half of every K slice of the tile
-        const uint32_t* recb = p.rec + ((size_t)mt * 2 * p.kb_total + half) * C * 128 + brow;
+        const uint32_t* recb = p.rec + (((size_t)mt * 2 * p.kb_total + half) * 128 + brow) * C;
         const uint16_t* cntb = p.cnt + ((size_t)mt * 2 * p.kb_total + half) * 128 + brow;
         auto load_cnt = [&](int kb) -> int {  // (rows at or beyond M of a partial last tile have zero counts)
           uint32_t n16 = 0u;
@@ -399,9 +399,13 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_cons
         // count of slice kb + 2 is requested for the next fetch into this register set
         auto fetch = [&](uint32_t(&r)[C], int& n, int& npre, int kb) {
           n = npre;
+          const uint4* rv = reinterpret_cast<const uint4*>(recb + (size_t)kb * 2 * 128 * C);
 #pragma unroll
-          for (int j = 0; j < C; ++j)
-            if (j < n) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[j]) : "l"(recb + ((size_t)kb * 2 * C + j) * 128));
+          for (int j = 0; j < C / 4; ++j)
+            if (4 * j < n)
+              asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(r[4 * j]), "=r"(r[4 * j + 1]), "=r"(r[4 * j + 2]), "=r"(r[4 * j + 3])
+                           : "l"(rv + j));
           npre = load_cnt(kb + 2);
         };
         auto fill = [&](int kb, const uint32_t(&r)[C], int n) -> bool {

@@ -43,7 +43,7 @@ struct PrologueParams {
   uint16_t* tail_idx16;
   uint16_t* tail_val;
   uint16_t* tail_ptr;  // [M, ptr_ld]: entries with index < 128 * j, j = 0 .. K/128
-  uint32_t* tail_rec;  // [2 ceil(M/256)][K/64][TQ_TAIL_REC_CAP][128]: tile position | bf16 << 16
+  uint32_t* tail_rec;  // [2 ceil(M/256)][K/64][128][TQ_TAIL_REC_CAP]: tile position | bf16 << 16
   uint16_t* tail_cnt;  // [2 ceil(M/256)][K/64][128]: entries per 64-wide half slice
   int32_t* idx32;
   int8_t* top_q;
@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
             if (jr < TQ_TAIL_REC_CAP)
               // bits 0..5: half the byte offset of the value inside its 128-byte row of the swizzled operand
               // tile (16-byte chunk index XOR row & 7, then the element); bits 16..31: the bf16 value
-              p.tail_rec[(((size_t)(m >> 7) * NHS + (i >> 6)) * TQ_TAIL_REC_CAP + jr) * 128 + (m & 127)] =
+              p.tail_rec[(((size_t)(m >> 7) * NHS + (i >> 6)) * 128 + (m & 127)) * TQ_TAIL_REC_CAP + jr] =
                   (uint32_t)(((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)) | (vb << 16);
           }
           if (p.top_q) st_q[pos] = (int8_t)quant_s4(bf16_bits_to_f32(vb), tscale, trinv);

@@ -6,8 +6,10 @@
 
 namespace tq {
 
+void set_last_error_text(const char* s);  // tq_api.cu
+
 // Status word of the pipelined kernels: 0, or the OR of the codes of the bounded waits that
-// ran out; read by tq_gemm_status().  The library is built as one translation unit
+// ran out; read (and cleared) by tq_gemm_status(), which callers poll at a synchronisation point.  The library is built as one translation unit
 // (tailquant.cu includes every kernel file), so there is exactly one copy.
 static __device__ unsigned int g_status = 0;
 
@@ -206,7 +208,10 @@ inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int esi
                                uint64_t inner, uint64_t outer, uint64_t pitch_bytes, int box_inner, int box_outer,
                                bool swizzle128 = false) {
   EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
+  if (!fn) {
+    set_last_error_text("cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
@@ -215,6 +220,8 @@ inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int esi
   CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    set_last_error_text("cuTensorMapEncodeTiled rejected a tensor map (base address, pitch or box of an operand)");
   return r == CUDA_SUCCESS;
 }
 

@@ -11,6 +11,8 @@ a forward is capturable in a CUDA graph after its first call, as the reference's
 """
 from __future__ import annotations
 
+import weakref
+from collections import OrderedDict
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -38,14 +40,19 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
 
 
 class _Workspace:
-    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool, n_out: Optional[int] = None):
+    """Buffers of one (layer, M): the prologue outputs (`pro`; absent in the workspace a layer uses when it runs on
+    another layer's prologue) and the layer's own output and scratch."""
+
+    def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool, n_out: Optional[int] = None,
+                 with_pro: bool = True):
         ld = (R + 7) // 8 * 8
         q8 = mma and not small  # the fused GEMM takes INT8 codes; the decode GEMV is faster on the packed form
-        self.pro = ops.PrologueOut(
+        self.M, self.K, self.R, self.q8 = M, K, R, q8
+        self.pro = None if not with_pro else ops.PrologueOut(
             a_pack=None if q8 else torch.empty((M, K // 2), dtype=torch.uint8, device=device),
             a_q8=torch.empty((M, K), dtype=torch.int8, device=device) if q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=device) if (mma and R) else None,
-            tail_rec=torch.empty((2 * ((M + 255) // 256), K // 64, ops.TAIL_REC_CAP, 128), dtype=torch.int32, device=device)
+            tail_rec=torch.empty((2 * ((M + 255) // 256), K // 64, 128, ops.TAIL_REC_CAP), dtype=torch.int32, device=device)
             if (mma and R) else None,
             tail_cnt=torch.zeros((2 * ((M + 255) // 256), K // 64, 128), dtype=torch.int16, device=device)
             if (mma and R) else None,
@@ -67,86 +74,99 @@ class SplitLinear:
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, ratio: float = 0.05,
                  activation_percentile: float = 100.0, had_kind: Optional[int] = None, small_m: int = 64,
                  split_k: int = 0, tail_engine: str = "mma", epilogue: str = "none",
-                 rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6):
+                 rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6, reuse_output: bool = True):
         """tail_engine: "mma" = tail on the tensor cores inside the GEMM kernel (default, fastest at
         ratios of a few percent); "gather" = exact-order fp32 fma chain on the CUDA cores (bit-exact
         against the CPU oracle, and the engine of the small-M path).
         epilogue: "swiglu" = `weight` is a fused gate_up matrix with interleaved rows (`interleave_gate_up`) and the
         layer returns bf16(bf16(silu(gate)) * up), [.., N/2], without writing the [.., N] intermediate.
         rms_weight: [K] bf16 weight of an RMSNorm that precedes this linear: the layer then takes the UN-normalised
-        hidden state and applies the norm inside its prologue kernel."""
+        hidden state and applies the norm inside its prologue kernel.
+        reuse_output: True (default) returns the layer's per-M output buffer, which the next forward with the same M
+        overwrites -- no allocation per call, what a captured CUDA graph needs; False returns a fresh tensor."""
         if tail_engine not in ("mma", "gather"):
             raise RuntimeError("tail_engine must be 'mma' or 'gather'")
         if epilogue not in ("none", "swiglu"):
             raise RuntimeError("epilogue must be 'none' or 'swiglu'")
         if epilogue == "swiglu" and (tail_engine != "mma" or weight.shape[0] % 16):
             raise RuntimeError("the SwiGLU epilogue needs the 'mma' tail engine and N % 16 == 0")
-        self.epilogue = epilogue
-        self.rms_weight = None if rms_weight is None else rms_weight.detach().to(torch.bfloat16).contiguous()
-        self.rms_eps = float(rms_eps)
-        self.tail_engine = tail_engine
         if not weight.is_cuda:
             raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
-        self.N, self.K = int(weight.shape[0]), int(weight.shape[1])
-        self.ratio = float(ratio)
-        self.R = ops.ceil_ratio_count(self.K, self.ratio)
-        _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
+        K = int(weight.shape[1])
+        R = ops.ceil_ratio_count(K, float(ratio))
         # the [K, N] transpose of the rotated weights serves the gather engine and the decode tail; with the
-        # tensor-core tail it is built on the first small-M call only (it doubles the bf16 weight memory)
-        self.w = ops.prepare_weight(weight, had_kind, t16=self.R > 0 and tail_engine == "gather",
-                                    keep_w_rot=self.R > 0 and tail_engine == "mma", bias=bias)
-        self.small_m = int(small_m)
-        self.split_k = int(split_k)
-        self.activation_percentile = float(activation_percentile)
-        self._ws: Dict[int, _Workspace] = {}
+        # tensor-core tail it is built by `prepare_decode()` or on the first small-M call (it doubles the bf16
+        # weight memory)
+        w = ops.prepare_weight(weight, had_kind, t16=R > 0 and tail_engine == "gather",
+                               keep_w_rot=R > 0 and tail_engine == "mma", bias=bias)
+        self._init(w, ratio, activation_percentile, small_m, split_k, tail_engine, epilogue,
+                   None if rms_weight is None else rms_weight.detach().to(torch.bfloat16).contiguous(), rms_eps,
+                   reuse_output)
 
-    @classmethod
-    def from_prepared(cls, w: "ops.PreparedWeight", ratio: float = 0.05, activation_percentile: float = 100.0,
-                      small_m: int = 64, split_k: int = 0, tail_engine: str = "mma") -> "SplitLinear":
-        """A layer around weights that are already rotated and quantised (e.g. read by `SplitLinear.load`)."""
-        if tail_engine not in ("mma", "gather"):
-            raise RuntimeError("tail_engine must be 'mma' or 'gather'")
-        if not w.b_col.is_cuda:
-            raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
-        self = cls.__new__(cls)
-        self.epilogue = "none"
-        self.rms_weight, self.rms_eps = None, 1e-6
-        self.tail_engine = tail_engine
+    def _init(self, w: "ops.PreparedWeight", ratio, activation_percentile, small_m, split_k, tail_engine, epilogue,
+              rms_weight, rms_eps, reuse_output) -> None:
+        self.w = w
         self.N, self.K = int(w.N), int(w.K)
         self.ratio = float(ratio)
         self.R = ops.ceil_ratio_count(self.K, self.ratio)
-        _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, activation_percentile)
-        if self.R > 0 and tail_engine == "mma" and w.w_rot is None:
-            raise RuntimeError("the tensor-core tail needs the rotated bf16 weights (w_rot)")
-        if self.R > 0 and tail_engine == "gather" and w.w_t is None and w.w_rot is not None:
-            w.w_t = w.w_rot.t().contiguous()  # the gather engine reads the [K, N] transpose
-        if self.R > 0 and w.w_t is None and w.w_rot is None:
-            raise RuntimeError("a tail needs the rotated bf16 weights (w_rot or w_t)")
-        self.w = w
-        self.small_m = int(small_m)
-        self.split_k = int(split_k)
-        self._ws = {}
         self.activation_percentile = float(activation_percentile)
+        _, self.descending_rank, _ = ops.split_select_params(self.K, self.R, self.activation_percentile)
+        self.small_m, self.split_k = int(small_m), int(split_k)
+        self.tail_engine, self.epilogue = tail_engine, epilogue
+        self.rms_weight, self.rms_eps = rms_weight, float(rms_eps)
+        self.reuse_output = bool(reuse_output)
+        self._ws: Dict[int, _Workspace] = {}
+        self._ws_shared: Dict[int, _Workspace] = {}
+
+    @classmethod
+    def from_prepared(cls, w: "ops.PreparedWeight", ratio: float = 0.05, activation_percentile: float = 100.0,
+                      small_m: int = 64, split_k: int = 0, tail_engine: str = "mma", epilogue: str = "none",
+                      rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
+                      reuse_output: bool = True) -> "SplitLinear":
+        """A layer around weights that are already rotated and quantised (e.g. read by `SplitLinear.load`)."""
+        if tail_engine not in ("mma", "gather"):
+            raise RuntimeError("tail_engine must be 'mma' or 'gather'")
+        if epilogue not in ("none", "swiglu"):
+            raise RuntimeError("epilogue must be 'none' or 'swiglu'")
+        if epilogue == "swiglu" and (tail_engine != "mma" or w.N % 16):
+            raise RuntimeError("the SwiGLU epilogue needs the 'mma' tail engine and N % 16 == 0")
+        if not w.b_col.is_cuda:
+            raise RuntimeError("SplitLinear needs CUDA weights: there is no CPU path")
+        R = ops.ceil_ratio_count(int(w.K), float(ratio))
+        if R > 0 and tail_engine == "mma" and w.w_rot is None:
+            raise RuntimeError("the tensor-core tail needs the rotated bf16 weights (w_rot)")
+        if R > 0 and tail_engine == "gather" and w.w_t is None and w.w_rot is not None:
+            w.w_t = w.w_rot.t().contiguous()  # the gather engine reads the [K, N] transpose
+        if R > 0 and w.w_t is None and w.w_rot is None:
+            raise RuntimeError("a tail needs the rotated bf16 weights (w_rot or w_t)")
+        self = cls.__new__(cls)
+        self._init(w, ratio, activation_percentile, small_m, split_k, tail_engine, epilogue,
+                   None if rms_weight is None else rms_weight.detach().to(device=w.b_col.device, dtype=torch.bfloat16).contiguous(),
+                   rms_eps, reuse_output)
         return self
 
     def save(self, path, policy_entry: Optional[dict] = None) -> None:
-        """Writes the prepared weights (packed INT4, scales, rotated bf16 rows, bias) to a `.tqw` file."""
+        """Writes the prepared weights (packed INT4, scales, rotated bf16 rows, bias) and what the layer fuses around
+        them (the epilogue kind, the RMSNorm weight and epsilon) to a `.tqw` file."""
         from . import weights_io
-        weights_io.save_prepared(path, self.w, ratio=self.ratio,
-                                 activation_percentile=getattr(self, "activation_percentile", 100.0),
-                                 policy_entry=policy_entry)
+        weights_io.save_prepared(path, self.w, ratio=self.ratio, activation_percentile=self.activation_percentile,
+                                 policy_entry=policy_entry, epilogue=self.epilogue, rms_weight=self.rms_weight,
+                                 rms_eps=self.rms_eps)
 
     @classmethod
     def load(cls, path, device="cuda", ratio: Optional[float] = None, tail_engine: str = "mma", small_m: int = 64,
              split_k: int = 0, policy_entry: Optional[dict] = None) -> "SplitLinear":
-        """Reads a `.tqw` file; ratio and percentile default to the ones stored in it."""
+        """Reads a `.tqw` file; ratio, percentile, epilogue and fused norm default to the ones stored in it."""
         from . import weights_io
         h = weights_io.read_header(path)
         w = weights_io.load_prepared(path, device, need_w_t=False, keep_w_rot=True, expect_policy_entry=policy_entry)
         r = h.get("ratio") if ratio is None else ratio
         return cls.from_prepared(w, ratio=0.0 if r is None else float(r),
                                  activation_percentile=float(h.get("activation_percentile") or 100.0),
-                                 small_m=small_m, split_k=split_k, tail_engine=tail_engine)
+                                 small_m=small_m, split_k=split_k, tail_engine=tail_engine,
+                                 epilogue=h.get("epilogue") or "none",
+                                 rms_weight=weights_io.load_extra(path, "rms_weight", device),
+                                 rms_eps=float(h.get("rms_eps") or 1e-6))
 
     def _use_mma(self, M: int) -> bool:
         return self.tail_engine == "mma" and M > self.small_m
@@ -162,13 +182,23 @@ class SplitLinear:
                                           M <= self.small_m, self.N_out)
         return ws
 
-    def _pick_split_k(self, M: int) -> int:
-        if self.split_k > 0:
-            return self.split_k
-        tiles = ((M + 127) // 128) * ((self.N + 127) // 128)
-        kb = self.K // 128
-        s = max(1, min(kb, (148 + tiles - 1) // tiles))
-        return s
+    def _own_buffers(self, ws: _Workspace, M: int) -> _Workspace:
+        """Output and scratch of THIS layer for a prologue workspace that may belong to another layer."""
+        if self._ws.get(M) is ws:
+            return ws
+        if (ws.K, ws.R, ws.M) != (self.K, self.R, M) or ws.q8 != self._use_mma(M):
+            raise RuntimeError("a shared prologue needs the same K, R, row count and operand format in both layers")
+        own = self._ws_shared.get(M)
+        if own is None:
+            own = self._ws_shared[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M),
+                                                  M <= self.small_m, self.N_out, with_pro=False)
+        return own
+
+    def prepare_decode(self) -> None:
+        """Builds the [K, N] transpose of the rotated weights that the small-M tail reads, ahead of the first small-M
+        forward (which otherwise builds it: an allocation inside that call)."""
+        if self.R and self.w.w_t is None:
+            self.w.w_t = self.w.w_rot.t().contiguous()
 
     def prologue(self, x2d: torch.Tensor) -> _Workspace:
         ws = self.workspace(x2d.shape[0])
@@ -177,41 +207,44 @@ class SplitLinear:
         return ws
 
     def compute(self, ws: _Workspace, M: int) -> torch.Tensor:
-        """GEMM + tail for a workspace whose prologue outputs are filled (shared-prologue use:
-        several linears with the same K, R and rank may run `compute` on one prologue, the way the
-        reference shares one prepare between q/k/v and gate/up:
-        tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:124-134)."""
+        """GEMM + tail for a workspace whose prologue outputs are filled.  `ws` may be ANOTHER layer's workspace
+        (shared-prologue use: several linears with the same K, R, rank and rotation run `compute` on one prologue,
+        the way the reference shares one prepare between q/k/v and gate/up:
+        tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:124-134); the output then goes to
+        this layer's own buffer of its own width."""
         w, pro = self.w, ws.pro
+        own = self._own_buffers(ws, M)
         if self._use_mma(M):
-            return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, ws.out, w_rot=w.w_rot, pro=pro,
+            return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, own.out, w_rot=w.w_rot, pro=pro,
                                       R=self.R, bias=w.bias, act=self.epilogue)
         if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
-            if ws.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
+            if own.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
                 splits = ops.gemv_plan(M, self.N, self.K)
-                ws.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=ws.out.device)
-            if self.R and w.w_t is None:
-                w.w_t = w.w_rot.t().contiguous()  # first small-M call of a layer prepared for the tensor-core tail
+                own.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=own.out.device)
+            self.prepare_decode()
             if self.R:
+                if own.tail is None:
+                    own.tail = torch.empty((M, self.N), dtype=torch.float32, device=own.out.device)
                 # the tail sums and the GEMV only depend on the prologue and neither fills the GPU at these sizes:
                 # the tail runs on a side stream next to the GEMV (a parallel branch when captured in a CUDA graph)
                 cur = torch.cuda.current_stream()
-                side = _side_stream(ws.out.device)
-                ws.ev_fork.record(cur)
-                side.wait_event(ws.ev_fork)
+                side = _side_stream(own.out.device)
+                own.ev_fork.record(cur)
+                side.wait_event(own.ev_fork)
                 with torch.cuda.stream(side):
-                    ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
-                    ws.ev_join.record(side)
-                ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
-                cur.wait_event(ws.ev_join)
+                    ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, own.tail, self.R)
+                    own.ev_join.record(side)
+                ops.gemv_partials(pro.a_pack, w.b_col, own.acc)
+                cur.wait_event(own.ev_join)
             else:
-                ops.gemv_partials(pro.a_pack, w.b_col, ws.acc)
-            ops.dequant_finish_partials(ws.acc, pro.body_scale, w.w_scale, ws.out, tail=ws.tail, bias=w.bias,
+                ops.gemv_partials(pro.a_pack, w.b_col, own.acc)
+            ops.dequant_finish_partials(own.acc, pro.body_scale, w.w_scale, own.out, tail=own.tail, bias=w.bias,
                                         act=self.epilogue)
-            return ws.out
+            return own.out
         if self.R:
-            ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, ws.tail, self.R)
-        ops.split_gemm_fused(pro.a_pack, pro.body_scale, w.b_col, w.w_scale, ws.out, tail=ws.tail, bias=w.bias)
-        return ws.out
+            ops.tail_gather(pro.tail_idx, pro.tail_val, w.w_t, own.tail, self.R)
+        ops.split_gemm_fused(pro.a_pack, pro.body_scale, w.b_col, w.w_scale, own.out, tail=own.tail, bias=w.bias)
+        return own.out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
@@ -222,30 +255,85 @@ class SplitLinear:
         M = x2d.shape[0]
         ws = self.prologue(x2d)
         y = self.compute(ws, M)
+        if not self.reuse_output:
+            y = y.clone()
         return y.view(*lead, self.N_out)
 
     __call__ = forward
 
 
-_CACHE: Dict[Tuple, SplitLinear] = {}
+# ------------------------------------------------------------------------------------------ adapter callable
+class _Entry:
+    __slots__ = ("lin", "wref", "bref", "shape", "ratio")
+
+
+_CACHE: "OrderedDict[Tuple, _Entry]" = OrderedDict()
+_CACHE_MAX = 1024        # prepared layers kept (a 36-layer model has 252 target linears)
+_SHARED: Dict[Tuple, Tuple] = {}  # (device, x ptr, x version, M, K, R, rank, rotation) -> (x weakref, workspace)
+
+
+def _drop(key) -> None:
+    _CACHE.pop(key, None)
+
+
+def clear_cache() -> None:
+    """Forgets every layer prepared by `split_linear_forward` (and frees their device memory)."""
+    _CACHE.clear()
+    _SHARED.clear()
+
+
+def _cached_layer(weight: torch.Tensor, bias: Optional[torch.Tensor], ratio: float) -> SplitLinear:
+    key = (weight.device.index, weight.data_ptr(), weight._version, tuple(weight.shape), float(ratio),
+           None if bias is None else (bias.data_ptr(), bias._version))
+    e = _CACHE.get(key)
+    # an address can be handed out again by the caching allocator after its tensor died: the entry only counts
+    # if it was built from THIS tensor object
+    if e is not None and e.wref() is weight and (bias is None or (e.bref is not None and e.bref() is bias)):
+        _CACHE.move_to_end(key)
+        return e.lin
+    e = _Entry()
+    e.lin = SplitLinear(weight, bias, ratio, reuse_output=True)
+    e.wref = weakref.ref(weight, lambda _r, k=key: _drop(k))  # the entry goes when the weight does
+    e.bref = None if bias is None else weakref.ref(bias)
+    _CACHE[key] = e
+    _CACHE.move_to_end(key)
+    while len(_CACHE) > _CACHE_MAX:
+        _CACHE.popitem(last=False)
+    return e.lin
 
 
 def split_linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                          ratio: float = 0.05, split_ratio: Optional[float] = None) -> torch.Tensor:
     """Callable the reference's adapter binds (tools/split_backend_adapter_v1.py:92-116): called as
-    fn(x [M,K], weight [N,K], bias=, ratio=) on every forward with the RAW weight, so prepared weights
-    are cached per (storage, version, shape, ratio).  Returns [M, N] in x's dtype.  The returned
-    tensor is a per-layer workspace that the next call of the same layer overwrites."""
+    fn(x [M,K], weight [N,K], bias=, ratio=) on every forward with the RAW weight, so prepared weights are cached
+    per weight tensor (object identity, version, shape, ratio; an entry dies with its weight, the cache is
+    bounded).  Returns a NEW [M, N] tensor in x's dtype, like the nn.Linear it stands in for.
+
+    Consecutive calls on the SAME input tensor by layers with the same K, R and rotation -- q/k/v, gate/up of a
+    model patched module by module -- share one prologue, the reference's shared prepare
+    (tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:221-261)."""
     if split_ratio is not None:
         ratio = split_ratio
     if bias is not None and not torch.is_tensor(bias):  # the adapter's positional form fn(x, W, ratio)
         ratio, bias = float(bias), None
     if weight.dim() != 2 or x.shape[-1] != weight.shape[1]:
         raise RuntimeError(f"weight must be [N, K] with K = x.shape[-1]; got {tuple(weight.shape)} for x {tuple(x.shape)}")
-    key = (weight.data_ptr(), weight._version, tuple(weight.shape), float(ratio),
-           None if bias is None else (bias.data_ptr(), bias._version))
-    lin = _CACHE.get(key)
-    if lin is None:
-        lin = _CACHE[key] = SplitLinear(weight, bias, ratio)
-    y = lin.forward(x)
+    lin = _cached_layer(weight, bias, ratio)
+    x2d = x.reshape(-1, lin.K)
+    if x2d.dtype != torch.bfloat16:
+        x2d = x2d.to(torch.bfloat16)
+    x2d = x2d.contiguous()
+    M = x2d.shape[0]
+    skey = (x.device.index, x2d.data_ptr(), x._version, M, lin.K, lin.R, lin.descending_rank, lin.w.had_kind,
+            lin._use_mma(M), torch.cuda.current_stream().cuda_stream)
+    hit = _SHARED.get(skey) if x2d.data_ptr() == x.data_ptr() else None
+    if hit is not None and hit[0]() is x:
+        ws = hit[1]
+    else:
+        ws = lin.prologue(x2d)
+        if x2d.data_ptr() == x.data_ptr():  # only inputs that were used as they are can be recognised again
+            _SHARED.clear()                  # one entry: the prologue outputs live in a workspace that the next
+            _SHARED[skey] = (weakref.ref(x), ws)  # prologue of that layer overwrites
+    y = lin.compute(ws, M).clone()
+    y = y.view(*x.shape[:-1], lin.N_out)
     return y if y.dtype == x.dtype else y.to(x.dtype)

@@ -28,7 +28,7 @@ from . import _lib
 from ._lib import TQ_BF16, TQ_FP16, TQ_HAD_BLOCK128, TQ_HAD_KRON12, TQ_HAD_NONE, TQ_HAD_WHT
 
 EPS = 1e-8
-TAIL_REC_CAP = 16  # TQ_TAIL_REC_CAP of include/tailquant.h
+TAIL_REC_CAP = 12  # TQ_TAIL_REC_CAP of include/tailquant.h
 
 
 # --------------------------------------------------------------------------- helpers
@@ -104,7 +104,7 @@ class PrologueOut:
     x_rot: Optional[torch.Tensor] = None  # [M, K] bf16
     a_q8: Optional[torch.Tensor] = None   # [M, K] i8, operand order of split_gemm_mma
     tail_ptr: Optional[torch.Tensor] = None  # [M, K/128 + 1] int16 storage of u16 run boundaries
-    tail_rec: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 16, 128] int32: tile position | bf16 << 16
+    tail_rec: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 128, TAIL_REC_CAP] int32: tile position | bf16 << 16
     tail_cnt: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 128] int16: entries per (row, 64-wide half slice)
 
 
@@ -131,7 +131,7 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
             R=R,
             a_q8=torch.empty((M, K), dtype=torch.int8, device=dev) if want_q8 else None,
             tail_ptr=torch.empty((M, K // 128 + 1), dtype=torch.int16, device=dev) if (want_q8 and R) else None,
-            tail_rec=torch.empty((2 * ((M + 255) // 256), K // 64, TAIL_REC_CAP, 128), dtype=torch.int32, device=dev)
+            tail_rec=torch.empty((2 * ((M + 255) // 256), K // 64, 128, TAIL_REC_CAP), dtype=torch.int32, device=dev)
             if (want_q8 and R) else None,
             tail_cnt=torch.zeros((2 * ((M + 255) // 256), K // 64, 128), dtype=torch.int16, device=dev)
             if (want_q8 and R) else None,
@@ -308,7 +308,7 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
         _check_cuda(tail_rec, "tail_rec", torch.int32)
         _check_cuda(tail_cnt, "tail_cnt", torch.int16)
         _check(tail_ptr.shape[0] == M and tail_ptr.shape[1] >= K // 128 + 1, "tail_ptr must be [M, K/128 + 1]")
-        _check(tuple(tail_rec.shape) == (2 * ((M + 255) // 256), K // 64, TAIL_REC_CAP, 128), "tail_rec has the wrong shape")
+        _check(tuple(tail_rec.shape) == (2 * ((M + 255) // 256), K // 64, 128, TAIL_REC_CAP), "tail_rec has the wrong shape")
         _check(tuple(tail_cnt.shape) == (2 * ((M + 255) // 256), K // 64, 128), "tail_cnt has the wrong shape")
         ld = tail_idx.shape[1]
     if bias is not None:

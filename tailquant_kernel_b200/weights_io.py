@@ -7,12 +7,14 @@ The reference re-quantises every linear at start-up (tools/bench_multimodel_all_
     bytes 8..15   u64    length H of the JSON header
     bytes 16..    H bytes of UTF-8 JSON:
                   {"N", "K", "had_kind", "eps", "ratio", "activation_percentile", "policy_hash",
+                   "epilogue", "rms_eps",
                    "tensors": {name: {"dtype", "shape", "offset", "nbytes", "crc32"}}}
     then the tensor payloads, each starting at its `offset` (from the start of the file, 256-byte aligned),
     raw row-major bytes.
 
 Stored tensors: `b_col` u8 [N, K/2] (packed INT4 codes, element 2i in the low nibble), `w_scale` f32 [N],
-and when present `w_rot` bf16 [N, K] (rotated weights, the tail operand), `b_row` u8 [K, N/2], `bias` f32 [N].
+and when present `w_rot` bf16 [N, K] (rotated weights, the tail operand), `b_row` u8 [K, N/2], `bias` f32 [N],
+`rms_weight` bf16 [K] (the RMSNorm a layer applies inside its prologue; `epilogue` names its fused activation).
 `w_t` ([K, N], the transpose of `w_rot`) is not stored: the loader rebuilds it when asked for.
 """
 from __future__ import annotations
@@ -50,8 +52,11 @@ def _raw_bytes(t: torch.Tensor) -> bytes:
 
 
 def save_prepared(path, w: PreparedWeight, ratio: Optional[float] = None, activation_percentile: float = 100.0,
-                  policy_entry: Optional[dict] = None, eps: Optional[float] = None) -> None:
+                  policy_entry: Optional[dict] = None, eps: Optional[float] = None, epilogue: str = "none",
+                  rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6) -> None:
     tensors = {"b_col": w.b_col, "w_scale": w.w_scale}
+    if rms_weight is not None:
+        tensors["rms_weight"] = rms_weight
     w_rot = w.w_rot if w.w_rot is not None else (w.w_t.t().contiguous() if w.w_t is not None else None)
     if w_rot is not None:
         tensors["w_rot"] = w_rot
@@ -61,7 +66,8 @@ def save_prepared(path, w: PreparedWeight, ratio: Optional[float] = None, activa
         tensors["bias"] = w.bias
     payloads = {k: _raw_bytes(v) for k, v in tensors.items()}
     header = {"N": int(w.N), "K": int(w.K), "had_kind": int(w.had_kind), "eps": eps, "ratio": ratio,
-              "activation_percentile": activation_percentile, "policy_hash": policy_hash(policy_entry), "tensors": {}}
+              "activation_percentile": activation_percentile, "policy_hash": policy_hash(policy_entry), "epilogue": epilogue,
+              "rms_eps": float(rms_eps), "tensors": {}}
     # the header's own length moves the offsets: lay it out with offsets as fixed-width numbers first
     for k, v in tensors.items():
         header["tensors"][k] = {"dtype": str(v.dtype).replace("torch.", ""), "shape": list(v.shape),
@@ -95,6 +101,36 @@ def read_header(path) -> dict:
         return json.loads(f.read(hlen).decode())
 
 
+def _read_tensor(f, path, name: str, d: dict, size: int, verify: bool, device) -> torch.Tensor:
+    if d["dtype"] not in _DTYPES:
+        raise RuntimeError(f"{path}: tensor {name} has unknown dtype {d['dtype']}")
+    if d["offset"] % _ALIGN or d["offset"] + d["nbytes"] > size:
+        raise RuntimeError(f"{path}: tensor {name} lies outside the file")
+    f.seek(d["offset"])
+    raw = f.read(d["nbytes"])
+    if len(raw) != d["nbytes"]:
+        raise RuntimeError(f"{path}: tensor {name} is truncated")
+    if verify and (zlib.crc32(raw) & 0xffffffff) != d["crc32"]:
+        raise RuntimeError(f"{path}: tensor {name} fails its checksum")
+    dt = _DTYPES[d["dtype"]]
+    np_dt = {torch.uint8: np.uint8, torch.float32: np.float32, torch.bfloat16: np.int16}[dt]
+    arr = np.frombuffer(raw, dtype=np_dt).reshape(d["shape"]).copy()
+    t = torch.from_numpy(arr)
+    if dt == torch.bfloat16:
+        t = t.view(torch.bfloat16)
+    return t.to(device)
+
+
+def load_extra(path, name: str, device="cuda", verify: bool = True) -> Optional[torch.Tensor]:
+    """One named tensor of a `.tqw` file (e.g. "rms_weight"), or None when the file does not hold it."""
+    path = Path(path)
+    d = read_header(path)["tensors"].get(name)
+    if d is None:
+        return None
+    with open(path, "rb") as f:
+        return _read_tensor(f, path, name, d, path.stat().st_size, verify, device)
+
+
 def load_prepared(path, device="cuda", need_w_t: bool = False, keep_w_rot: bool = True, verify: bool = True,
                   expect_policy_entry: Optional[dict] = None) -> PreparedWeight:
     """Reads a `.tqw` file onto `device`.  `need_w_t` rebuilds the [K, N] transpose (gather engine and decode tail);
@@ -107,23 +143,7 @@ def load_prepared(path, device="cuda", need_w_t: bool = False, keep_w_rot: bool 
     out = {}
     with open(path, "rb") as f:
         for name, d in h["tensors"].items():
-            if d["dtype"] not in _DTYPES:
-                raise RuntimeError(f"{path}: tensor {name} has unknown dtype {d['dtype']}")
-            if d["offset"] % _ALIGN or d["offset"] + d["nbytes"] > size:
-                raise RuntimeError(f"{path}: tensor {name} lies outside the file")
-            f.seek(d["offset"])
-            raw = f.read(d["nbytes"])
-            if len(raw) != d["nbytes"]:
-                raise RuntimeError(f"{path}: tensor {name} is truncated")
-            if verify and (zlib.crc32(raw) & 0xffffffff) != d["crc32"]:
-                raise RuntimeError(f"{path}: tensor {name} fails its checksum")
-            dt = _DTYPES[d["dtype"]]
-            np_dt = {torch.uint8: np.uint8, torch.float32: np.float32, torch.bfloat16: np.int16}[dt]
-            arr = np.frombuffer(raw, dtype=np_dt).reshape(d["shape"]).copy()
-            t = torch.from_numpy(arr)
-            if dt == torch.bfloat16:
-                t = t.view(torch.bfloat16)
-            out[name] = t.to(device)
+            out[name] = _read_tensor(f, path, name, d, size, verify, device)
     N, K = int(h["N"]), int(h["K"])
     if tuple(out["b_col"].shape) != (N, K // 2) or tuple(out["w_scale"].shape) != (N,):
         raise RuntimeError(f"{path}: tensor shapes disagree with N = {N}, K = {K}")

@@ -294,14 +294,14 @@ def _output_bounds(y_bits, y32, slack=0.0):
     assert err.sum() / np.abs(y32).sum() <= 1e-2
 
 
-def tail_records(idx, val_bits, K, cap=16):
+def tail_records(idx, val_bits, K, cap=12):
     """The regrouped tail lists the fused GEMM reads: run boundaries per 128-wide slice, records and counts per
     64-wide half slice."""
     M, R = idx.shape
     KB, KH, TM = K // 128, K // 64, 2 * ((M + 255) // 256)
     ptr = np.stack([np.searchsorted(idx[m].astype(np.int64), np.arange(KB + 1, dtype=np.int64) * 128, side="left")
                     for m in range(M)]).astype(np.uint16) if M else np.zeros((0, KB + 1), np.uint16)
-    rec = np.zeros((TM, KH, cap, 128), np.uint32)
+    rec = np.zeros((TM, KH, 128, cap), np.uint32)
     cnt = np.zeros((TM, KH, 128), np.uint16)
     for m in range(M):
         hb = np.searchsorted(idx[m].astype(np.int64), np.arange(KH + 1, dtype=np.int64) * 64, side="left")
@@ -311,7 +311,7 @@ def tail_records(idx, val_bits, K, cap=16):
             for j in range(min(b - a, cap)):
                 i = int(idx[m, a + j])
                 pos = ((((i & 63) >> 3) ^ (m & 7)) << 3) | (i & 7)
-                rec[m >> 7, h, j, m & 127] = pos | (int(val_bits[m, a + j]) << 16)
+                rec[m >> 7, h, m & 127, j] = pos | (int(val_bits[m, a + j]) << 16)
     return ptr, rec, cnt
 
 
@@ -336,7 +336,7 @@ def test_prologue_int8_operand(kind, K, M, R):
         assert np.array_equal(host_bits(out.tail_ptr), ptr), "run boundaries"
         assert np.array_equal(host_bits(out.tail_cnt), cnt), "entries per slice"
         got = out.tail_rec.cpu().numpy().view(np.uint32)
-        valid = np.arange(16).reshape(1, 1, 16, 1) < np.minimum(cnt, 16)[:, :, None, :]
+        valid = np.arange(12).reshape(1, 1, 1, 12) < np.minimum(cnt, 12)[:, :, :, None]
         assert np.array_equal(got[valid], rec[valid]), "slice records"
     both = ops.split_prologue(dev_bf16(xb), kind, R, want_q8=True)
     assert np.array_equal(both.a_pack.cpu().numpy(), ref.a_pack)
@@ -554,6 +554,82 @@ def test_full_size_properties_qwen3_layer_shapes():
         C = ops.matmul(out.a_pack, b_col)
         ref = torch._int_mm(codes.contiguous(), wq.t().contiguous())
         assert torch.equal(C, ref)
+
+
+BENCH_SHAPES = [
+    # name, M, K, N, rotation, R, outlier channels: the four linears of baseline config 2 (Qwen3-8B layer, M = 2048,
+    # ratio 0.05: what bench.py times) and the widest-K case of config 4 (Llama-3 down_proj, M = 4096, block-128
+    # rotation, 1 % outlier channels)
+    ("qkv_proj", 2048, 4096, 6144, O.HAD_WHT, 205, 16),
+    ("o_proj", 2048, 4096, 4096, O.HAD_WHT, 205, 16),
+    ("gate_up_proj", 2048, 4096, 24576, O.HAD_WHT, 205, 16),
+    ("down_proj", 2048, 12288, 4096, O.HAD_KRON12, 615, 16),
+    ("llama_down_proj", 4096, 14336, 4096, O.HAD_BLOCK128, 717, 143),
+]
+
+
+def sample_rows(M):
+    """Rows {0, 127, 128, 255} of the first, a middle and the last 256-row tile."""
+    tiles = sorted({0, (M // 256) // 2, (M + 255) // 256 - 1})
+    rows = [t * 256 + r for t in tiles for r in (0, 127, 128, 255) if t * 256 + r < M]
+    return np.array(sorted(set(rows)), dtype=np.int64)
+
+
+def sample_channels(N):
+    """Every channel of the first, a middle and the last 256-wide column tile."""
+    tiles = sorted({0, (N // 256) // 2, (N + 255) // 256 - 1})
+    return np.concatenate([np.arange(t * 256, min(N, t * 256 + 256)) for t in tiles]).astype(np.int64)
+
+
+@pytest.mark.parametrize("name,M,K,N,kind,R,n_out", BENCH_SHAPES)
+def test_fused_gemm_at_benchmark_shapes(name, M, K, N, kind, R, n_out):
+    """The kernel and the shapes bench.py times: the layer object with its default engine and default dispatch (the
+    CTA-pair kernel at these sizes, many tiles per pair, 32 to 112 K slices per tile), checked on sampled rows and
+    output channels against the CPU oracle (rows and output channels are independent in every stage, so the oracle
+    only has to work through the sample): prologue outputs and int32 accumulators bit for bit, bf16 outputs inside
+    the stated bounds.  Comparison per tools/compare_single_matrix_fake_vs_kernel_quant_l2_v1.py:58-97."""
+    from tailquant_kernel_b200 import SplitLinear
+    assert ((M + 127) // 128) * ((N + 255) // 256) > 74, "the default dispatch must pick the CTA-pair kernel here"
+    xb = O.make_activations(M, K, seed=17, n_outlier=n_out)
+    wb = O.make_weights(N, K, seed=23)
+    rows, chan = sample_rows(M), sample_channels(N)
+    lin = SplitLinear(dev_bf16(wb), ratio=R / K, had_kind=kind)
+    assert lin.R == R
+    x = dev_bf16(xb)
+    y = lin(x)
+    ws = lin.workspace(M)
+    dacc = torch.empty((M, N), dtype=torch.int32, device="cuda")
+    dtail = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    y2 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    ops.split_gemm_mma(ws.pro.a_q8, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, y2, w_rot=lin.w.w_rot, pro=ws.pro,
+                       R=R, dbg_acc=dacc, dbg_tail=dtail)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2), "the run with the debug outputs must give the same bf16 bits"
+    # ---- oracle on the sample
+    wq = O.prepare_weight(wb[chan], kind)
+    ref = O.prologue(xb[rows], kind, R)
+    acc = O.int_gemm(ref.codes, wq)
+    tail = O.tail_t16(ref.idx, ref.tail_val, wq)
+    y32 = (O.dequant(acc, ref.body_scale, wq.w_scale) + tail).astype(np.float32)
+    r_t, c_t = torch.from_numpy(rows).cuda(), torch.from_numpy(chan).cuda()
+    # weight prep of the sampled channels
+    assert np.array_equal(lin.w.b_col[c_t].cpu().numpy(), wq.b_col), "INT4 weight codes"
+    assert np.array_equal(lin.w.w_scale[c_t].cpu().numpy(), wq.w_scale), "weight scales"
+    assert np.array_equal(host_bits(lin.w.w_rot[c_t]), wq.w_rot), "rotated bf16 weight rows"
+    # prologue of the sampled rows
+    assert np.array_equal(ws.pro.a_q8[r_t].cpu().numpy(), permute_q8(ref.codes)), "INT4 codes of the activations"
+    assert np.array_equal(ws.pro.body_scale[r_t].cpu().numpy(), ref.body_scale), "body scales"
+    assert np.array_equal(host_bits(ws.pro.tail_idx[r_t])[:, :R].astype(np.int32), ref.idx), "tail indices"
+    assert np.array_equal(host_bits(ws.pro.tail_val[r_t])[:, :R], ref.tail_val), "tail values"
+    # accumulators, tail sums, outputs
+    assert np.array_equal(dacc[r_t][:, c_t].cpu().numpy(), acc), "int32 accumulators"
+    scale = np.abs(O.bf16_bits_to_f32(ref.tail_val)).max() * np.abs(O.bf16_bits_to_f32(wq.w_rot)).max() * R
+    got_tail = dtail[r_t][:, c_t].cpu().numpy()
+    assert np.abs(got_tail - tail).max() <= 1e-5 * scale, "tensor-core tail vs fixed-order fp32 chain"
+    yb = host_bits(y[r_t][:, c_t])
+    _output_bounds(yb, y32, slack=1e-5 * scale)
+    diff = yb != O.f32_to_bf16_bits(y32)
+    assert diff.mean() < 0.01, f"{diff.mean():.4f} of the sampled outputs differ from bf16(oracle)"
 
 
 @pytest.mark.gpu
