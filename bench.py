@@ -36,16 +36,28 @@ LAYER = [  # name, K, N
 ]
 M_TOKENS = 2048
 RATIO = 0.05
-CPU_SAMPLE_ROWS = 64
+CPU_SAMPLE_ROWS = 256
 METRIC = "split W4A4+tail linear TOPS, Qwen3-8B layer shapes, prefill M=2048/GPU, ratio 0.05"
 NOMINAL_INT8_TOPS = 4500.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the four pair_gemm_kernel launches of one step (gate_up, down,
-# qkv, o), from the ncu capture summarised in profiles/pair_gemm_kernel_qwen3_layer_m2048.md (bytes)
-PAIR_GEMM_DRAM_BYTES_PER_STEP = int((279.1 + 86.0 + 235.3 + 13.6 + 81.1 + 9.5 + 59.5 + 2.2) * 1e6)
+
+
+def measured_dram_traffic(kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one step's launches of `kernel`, from the table that is kept
+    beside the profile summaries and rewritten whenever the kernel is captured again (None when it has no entry)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            e = json.load(f).get(kernel)
+        return int(e["bytes_per_step"]) if e else None
+    except Exception:
+        return None
 
 
 def layer_ops(m: int) -> float:
     return float(sum(2.0 * m * n * k for _, k, n in LAYER))
+
+
+def ops_step_of(m: int) -> float:
+    return layer_ops(m)
 
 
 def load_peaks():
@@ -75,19 +87,29 @@ def cpu_oracle_step(O, ws):
         O.split_linear_t16(x, w, kind, R)
 
 
-def cpu_threads() -> int:
+def use_all_host_threads() -> int:
+    """Gives the BLAS under numpy every core of the box and says how many it got.  A launcher (torchrun) exports
+    OMP_NUM_THREADS=1 to its workers, so the count is set explicitly: in the environment when numpy is not loaded
+    yet, through threadpoolctl in any case."""
+    n = os.cpu_count() or 1
+    if "numpy" not in sys.modules:
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = str(n)
     try:
-        from threadpoolctl import threadpool_info
-        n = max([int(p.get("num_threads", 1)) for p in threadpool_info()] or [1])
-        return max(n, 1)
+        import numpy  # noqa: F401
+        from threadpoolctl import threadpool_info, threadpool_limits
+        threadpool_limits(limits=n)
+        got = max([int(p.get("num_threads", 1)) for p in threadpool_info()] or [1])
+        return max(got, 1)
     except Exception:
-        return os.cpu_count() or 1
+        return n
 
 
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cores = use_all_host_threads()
     O, ws = cpu_oracle_setup()
     for _ in range(args.warmup):
         cpu_oracle_step(O, ws)
@@ -104,9 +126,12 @@ def run_reference(args) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 x int4 -> int32, fp32 dequant, bf16 out",
         "data": "synthetic",
-        "config": {"workload": "Qwen3-8B decoder layer linears (BASELINE configs[1])", "rows_per_step": CPU_SAMPLE_ROWS,
-                   "tail_ratio": RATIO},
-        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "config": {"workload": "Qwen3-8B decoder layer linears: qkv 4096->6144, o 4096->4096, gate_up 4096->24576, "
+                               "down 12288->4096 (BASELINE configs[1])",
+                   "rows_per_step": CPU_SAMPLE_ROWS, "rows_of_the_gpu_arm": M_TOKENS, "tail_ratio": RATIO,
+                   "same_config": CPU_SAMPLE_ROWS == M_TOKENS,
+                   "note": "a bounded sample of the rows; throughput (TOPS) is per row and comparable, ms_per_step is not"},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -371,16 +396,67 @@ def run_ours(args) -> None:
     graph_bf16_ms = graph_median_ms(step_bf16)
     del Wbs
 
+    # ---- plain pinned copies of one step's inputs and outputs, no compute: the ceiling of the end-to-end figure
+    def copy_only():
+        with torch.cuda.stream(s_in):
+            for hx, dx in zip(host_x, dev_x):
+                dx.copy_(hx, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for hy, dy in zip(host_y, dev_y):
+                hy.copy_(dy, non_blocking=True)
+
+    ms_copy, _ = timed(copy_only, max(args.steps // 2, 3), 3, drain=drain_e2e)
+
+    # ---- N > 1: the same 2048 rows cut over the ranks (strong scaling), and the column-parallel gate_up
+    strong, colpar = None, None
+    if world > 1:
+        rows = M_TOKENS // world
+        xs_s = [x[rank * rows:(rank + 1) * rows].contiguous() for x in xs]
+
+        def step_strong():
+            for lin, x in zip(lins, xs_s):
+                lin.forward(x)
+
+        ms_strong, _ = timed(step_strong, args.steps, args.warmup)
+        strong = {"rows_per_gpu": rows, "ms_per_step": ms_strong, "tops": ops_step_of(M_TOKENS) / (ms_strong * 1e-3) / 1e12,
+                  "speedup_over_one_gpu": ms_step / ms_strong, "efficiency": ms_step / ms_strong / world,
+                  "note": "M = 2048 rows of the layer cut into contiguous slabs, one per GPU, no collective; one GPU's "
+                          "time for all 2048 rows is this run's ms_per_step.  A 256-row slab is a single row of "
+                          "256 x 256 tiles: 16 to 96 tiles for 74 CTA pairs, so most of the GPU idles at N = 8"}
+        from tailquant_kernel_b200 import shard
+        name, Kg, Ng = LAYER[2]
+        gen.manual_seed(100 + 2)
+        Wg = (torch.randn((Ng, Kg), generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(dev)
+        cp = shard.ColumnParallelSplitLinear(Wg, rank, world, ratio=RATIO, had_kind=TQ_HAD_WHT)
+        del Wg
+        xg = xs[2] if rank == 0 else torch.empty_like(xs[2])
+        dist.broadcast(xg, 0)  # column parallelism works on the SAME rows on every rank
+        y_cp = cp.forward(xg)
+        y_full = lins[2].forward(xg)
+        cp_equal = bool(torch.equal(y_cp, y_full))
+        ms_cp, _ = timed(lambda: cp.forward(xg), args.steps, args.warmup)
+        ms_cp_gemm, _ = timed(lambda: cp.local.forward(xg), args.steps, args.warmup)
+        ms_row, _ = timed(lambda: lins[2].forward(xs_s[2]), args.steps, args.warmup)
+        ms_one, _ = timed(lambda: lins[2].forward(xs[2]), args.steps, args.warmup)
+        colpar = {"linear": name, "rows": M_TOKENS, "columns_per_gpu": Ng // world,
+                  "ms_linear_plus_all_gather": ms_cp, "ms_linear_only": ms_cp_gemm,
+                  "ms_all_gather": ms_cp - ms_cp_gemm, "gathered_bytes_per_gpu": 2 * M_TOKENS * (Ng - Ng // world),
+                  "ms_row_sharded_same_work": ms_row, "ms_one_gpu": ms_one, "equals_unsplit_layer": cp_equal,
+                  "note": "gate_up cut over output channels, one NCCL all_gather_into_tensor of the bf16 slabs over NVLink; "
+                          "the row shard needs no exchange at all and is the default"}
+
     peaks = load_peaks()
     ops_step = layer_ops(M_TOKENS)
-    int8_peak = 2.0 * peaks["bf16_sustained"]  # no INT8 peak was measured: twice the sustained bf16 matmul figure
+    # no INT8 peak was measured: twice the bf16 matmul figure -- the burst one, because the roofline entry times its
+    # kernel in isolation (ten launches, a few milliseconds: the clocks stay at their maximum, see `clocks`)
+    int8_peak = 2.0 * peaks["bf16"]
     gemm_tops = ops_step / (t_gemm * 1e-3) / 1e12
     pro_bytes = sum(M_TOKENS * (2 * K + (K if mma else K // 2) + 4 * lin.R + 4) for (_, K, _), lin in zip(LAYER, lins))
     pro_gbs = pro_bytes / (t_pro * 1e-3) / 1e9
     tail_flops = sum(2.0 * M_TOKENS * lin.R * N for (_, K, N), lin in zip(LAYER, lins))
     # tensor-pipe time the kernel's MMAs need at the measured library rates: the int8 product, plus (tensor-core
     # tail) a dense bf16 product of the same shape over the zero-filled tail matrix
-    pipe_ms = ops_step / (int8_peak * 1e12) * 1e3 + (ops_step / (peaks["bf16_sustained"] * 1e12) * 1e3 if mma else 0.0)
+    pipe_ms = ops_step / (int8_peak * 1e12) * 1e3 + (ops_step / (peaks["bf16"] * 1e12) * 1e3 if mma else 0.0)
     t_sum = t_gemm + t_tail + t_pro
 
     h2d = sum(int(h.numel() * h.element_size()) for h in host_x)
@@ -415,16 +491,20 @@ def run_ours(args) -> None:
                    "rows_per_gpu": M_TOKENS, "global_rows": M_TOKENS * world, "tail_ratio": RATIO,
                    "tail_engine": args.tail_engine,
                    "parallelism": f"token-row shard x{world}, replicated weights, no collective",
-                   "l2": "per-step working set (96 MB int4 + 192 MB bf16 weights, 260 MB activations/outputs) exceeds the 126 MB L2"},
+                   "l2": "per-step working set (96 MB int4 + 386 MB bf16 weights, 260 MB activations/outputs) exceeds the 126 MB L2"},
         "e2e": {"value": ops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "copy_only_ms_per_step": ms_copy,
+                "copy_only_gbs_all_gpus": (h2d + d2h) * world / (ms_copy * 1e-3) / 1e9,
+                "note": "copy_only = the same pinned host<->device copies of one step with no compute between them "
+                        "(both directions at once, all ranks together): the ceiling the end-to-end figure sits under"},
         "gpu_launches": (8 if mma else 12) * args.steps,
         "clocks": clocks,
         "roofline": {"kernel": kname, "bound": "tensor",
                      "achieved": dom_tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": dom_tops / int8_peak,
                      "ms_per_step_in_kernel": dom_ms,
-                     "traffic": PAIR_GEMM_DRAM_BYTES_PER_STEP if mma else None,
-                     "peak_note": f"2 x sustained bf16 cuBLAS figure ({peaks['source']}); nominal dense INT8 {NOMINAL_INT8_TOPS}; "
+                     "traffic": measured_dram_traffic("pair_gemm_kernel") if mma else None,
+                     "peak_note": f"2 x burst bf16 cuBLAS figure ({peaks['source']}; the kernel is timed alone); nominal dense INT8 {NOMINAL_INT8_TOPS}; "
                                   "achieved counts the algorithmic 2*M*N*K of the INT4 product only",
                      "frac_of_nominal_int8": dom_tops / NOMINAL_INT8_TOPS,
                      "all_gemm_launches_tops": gemm_tops,
@@ -443,21 +523,50 @@ def run_ours(args) -> None:
                           "split_over_bf16": graph_split_ms / graph_bf16_ms,
                           "protocol": "one CUDA graph per layer (4 linears), 5 warm-ups, 30 replays, median of 5 runs"},
     }
+    if strong is not None:
+        line["strong"] = strong
+        line["column_parallel"] = colpar
     if not mma:
         line["kernels"]["tail_gather"] = {"ms_per_step": t_tail, "share": t_tail / t_sum,
                                           "gflops": tail_flops / (t_tail * 1e-3) / 1e9,
                                           "bound": "CUDA-core fma + shared-memory gathers"}
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = use_all_host_threads()
         O, ws = cpu_oracle_setup()
         cpu_oracle_step(O, ws)
         t0 = time.perf_counter()
-        reps = 4
+        reps = 2
         for _ in range(reps):
             cpu_oracle_step(O, ws)
         dt = (time.perf_counter() - t0) / reps
+        # ---- one sampled row per 1024 and 256 output channels of every linear against the oracle (as the checker)
+        import numpy as np
+        worst, frac = 0.0, 0.0
+        for i, ((name, K, N), lin) in enumerate(zip(LAYER, lins)):
+            rows_s = np.array([0, M_TOKENS // 2 - 1, M_TOKENS - 1])
+            chan = np.concatenate([np.arange(0, 128), np.arange(N - 128, N)])
+            gen.manual_seed(100 + i)
+            Wc = (torch.randn((N, K), generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            wb = Wc[torch.from_numpy(chan)].contiguous().view(torch.int16).numpy().view(np.uint16)
+            del Wc
+            xb = host_x[i][torch.from_numpy(rows_s)].contiguous().view(torch.int16).numpy().view(np.uint16)
+            kind = O.HAD_KRON12 if K == 12288 else O.HAD_WHT
+            y_ref, y32, _, _ = O.split_linear_t16(xb, O.prepare_weight(wb, kind), kind, lin.R)
+            y = lin.forward(xs[i])[torch.from_numpy(rows_s).to(dev)][:, torch.from_numpy(chan).to(dev)]
+            got = O.bf16_bits_to_f32(y.contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+            err = np.abs(got.astype(np.float64) - y32.astype(np.float64))
+            half_ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(y32), 1e-30))) - 8)
+            assert bool(np.all(err <= np.maximum(2e-2, half_ulp * (1 + 1e-6) + 1e-3))), f"parity: {name} leaves the output bounds"
+            assert err.sum() / np.abs(y32).sum() <= 1e-2, f"parity: {name} mean relative error"
+            worst = max(worst, float(err.max()))
+            frac = max(frac, float((O.f32_to_bf16_bits(got) != y_ref).mean()))
+        line["parity_checked"] = True
+        line["parity"] = {"rows_per_linear": 3, "channels_per_linear": 256, "max_abs_err_vs_fp32_oracle": worst,
+                          "worst_fraction_not_equal_to_bf16_of_oracle": frac,
+                          "bounds": "max-abs <= max(2e-2, half an output ulp), mean-rel <= 1e-2"}
         line["cpu_baseline"] = {
-            "value": layer_ops(CPU_SAMPLE_ROWS) / dt / 1e12, "unit": "TOPS", "cores": cpu_threads(), "kind": "port",
+            "value": layer_ops(CPU_SAMPLE_ROWS) / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
             "sample": f"numpy oracle, online path of all four linears on {CPU_SAMPLE_ROWS} of the 2048 rows, mean of {reps} passes"}
     if rank == 0:
         print(json.dumps(line), flush=True)

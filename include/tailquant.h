@@ -94,8 +94,9 @@ int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int desc
  * PyTorch module before the linear: tools/bench_layer_async_schedule_v22.py:237,249 -- `layer.input_layernorm`,
  * `layer.post_attention_layernorm`; x is the un-normalised hidden state, gamma the [K] bf16 norm weight):
  *   x_n[m,k] = bf16( bf16( x[m,k] / sqrt(mean_k(x[m,:]^2) + rms_eps) ) * gamma[k] ),
- * the squares summed in fp32 in a fixed order (16 consecutive elements per thread, a butterfly over 32 threads,
- * eight partial sums in order), then everything as in tq_split_prologue on x_n.  No [M,K] normalised tensor is
+ * the squares summed in fp32 in a fixed order (K = 4096, 12288, 14336: thread t of K/64 adds its 64 consecutive
+ * elements in index order; other K: thread t of 256 adds 16-element chunks t, t + 256, ...; then a butterfly over the
+ * 32 threads of a warp and the warp sums in order), then everything as in tq_split_prologue on x_n.  No [M,K] normalised tensor is
  * written.  (T4 outputs idx32 / top_q are not offered here.) */
 int tq_split_prologue_rmsnorm(const void* x, const void* gamma, float rms_eps, int M, int K, int had_kind, int R,
                               int descending_rank, float eps, uint8_t* a_pack, int8_t* a_q8, float* body_scale,
@@ -108,8 +109,9 @@ int tq_split_prologue_rmsnorm(const void* x, const void* gamma, float rms_eps, i
  *   tools/fused_topr_pack_ext_v55.py:112-121
  * threshold_topr_pack(<same>)
  *   tools/fused_threshold_topr_pack_ext_v57.py:236-245
- * Both names map here; indices are written in ascending order. `dtype` is TQ_BF16
- * (TQ_FP16, the reference's input type, is answered with TQ_ERR_UNSUPPORTED). */
+ * Both names map here; indices are written in ascending order. `dtype` is TQ_BF16, or TQ_FP16 (the reference's
+ * input type: the same select on the 15-bit magnitude of the half, tools/fused_threshold_topr_pack_ext_v57.py:32-35)
+ * for K = 4096 and 12288, the widths the reference builds (same file :258-259). */
 int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int descending_rank,
                  uint8_t* A_pack, float* body_scale, float* top_scale, int8_t* top_q, int32_t* idx,
                  float eps, void* stream);
@@ -189,6 +191,12 @@ int tq_split_gemm_mma_swiglu(const int8_t* a_q8, const float* body_scale, const 
  * without a tail or when there are more than 74 one-CTA tiles), 0 / 1 force one of them.  A tuning knob without
  * a reference counterpart. */
 int tq_set_gemm_pair_mode(int mode);
+
+/* The prologue has two kernels with identical outputs: one specialised for K = 4096, 12288 and 14336 (a thread per
+ * 64 contiguous elements, the row staged by one TMA load) and a general one for every other built width.  mode -1
+ * (default) uses the specialised kernel where it applies, 0 forces the general one.  A comparison switch without a
+ * reference counterpart. */
+int tq_set_prologue_mode(int mode);
 
 /* Finisher of the split-K path: out = bf16((float(C)*body_scale[m])*w_scale[n] + tail + bias). */
 int tq_dequant_finish(const int32_t* C, const float* body_scale, const float* w_scale,

@@ -206,9 +206,13 @@ def select_tail(x_bits: np.ndarray, R: int, descending_rank: Optional[int] = Non
 
 
 # ----------------------------------------------------------------------------- quantise
-def act_scale(key_bits: np.ndarray, eps: float = EPS) -> np.ndarray:
+def f16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(b, dtype=np.uint16).view(np.float16).astype(np.float32)
+
+
+def act_scale(key_bits: np.ndarray, eps: float = EPS, fmt: str = "bf16") -> np.ndarray:
     """max(threshold, eps) / 7 in fp32 (tools/fused_topr_pack_ext_v55.py:76-79)."""
-    t = bf16_bits_to_f32(key_bits)
+    t = bf16_bits_to_f32(key_bits) if fmt == "bf16" else f16_bits_to_f32(key_bits)
     return (np.maximum(t, np.float32(eps)) / np.float32(7.0)).astype(np.float32)
 
 
@@ -249,13 +253,17 @@ class Prologue:
 
 
 def prologue(x_bits: np.ndarray, kind: int, R: int, descending_rank: Optional[int] = None,
-             eps: float = EPS) -> Prologue:
+             eps: float = EPS, fmt: str = "bf16") -> Prologue:
+    """fmt = "fp16": the rows are IEEE half bits (the reference kernels' input type,
+    tools/fused_threshold_topr_pack_ext_v57.py:32-35: the same 15-bit magnitude keys); no rotation then."""
+    if fmt not in ("bf16", "fp16") or (fmt == "fp16" and kind != HAD_NONE):
+        raise ValueError("fp16 rows are taken as they are (kind = HAD_NONE)")
     xr = rotate_bf16(x_bits, kind)
     M, K = xr.shape
     sel = select_tail(xr, R, descending_rank)
-    xf = bf16_bits_to_f32(xr)
-    bscale = act_scale(sel.body_key, eps)
-    tscale = act_scale(sel.top_key, eps)
+    xf = bf16_bits_to_f32(xr) if fmt == "bf16" else f16_bits_to_f32(xr)
+    bscale = act_scale(sel.body_key, eps, fmt)
+    tscale = act_scale(sel.top_key, eps, fmt)
     codes = quant_s4(xf, bscale)
     codes[sel.tail_mask] = 0
     if R:
@@ -367,20 +375,29 @@ def split_linear_t16(x_bits: np.ndarray, w: PreparedWeight, kind: int, R: int,
     return f32_to_bf16_bits(y), y, p, acc
 
 
-def rmsnorm_bf16(x_bits: np.ndarray, gamma_bits: np.ndarray, eps: float = 1e-6, threads: int = 256) -> np.ndarray:
+def rmsnorm_sum_layout(K: int) -> Tuple[int, int]:
+    """(threads, chunk) of the sum of squares inside the fused prologue: the widths that have the specialised
+    kernel (one thread per 64 contiguous elements) and the general kernel (256 threads, 16-element chunks)."""
+    return (K // 64, 64) if K in (4096, 12288, 14336) else (256, 16)
+
+
+def rmsnorm_bf16(x_bits: np.ndarray, gamma_bits: np.ndarray, eps: float = 1e-6, threads: Optional[int] = None,
+                 chunk: Optional[int] = None) -> np.ndarray:
     """RMSNorm of bf16 rows as a bf16 framework rounds it (x * rsqrt(mean(x^2) + eps) in fp32 -> bf16, times the
     bf16 weight -> bf16; e.g. transformers' Qwen3RMSNorm), with the fp32 sum of squares taken in the order of the
-    fused prologue kernel: thread t adds the squares of elements [16 w, 16 w + 16) for w = t, t + threads, ... one
-    after the other, a butterfly (xor 16, 8, 4, 2, 1) adds the 32 threads of a warp, and the warp sums are added in
-    order."""
+    fused prologue kernel: thread t adds the squares of elements [chunk w, chunk w + chunk) for w = t, t + threads,
+    ... one after the other, a butterfly (xor 16, 8, 4, 2, 1) adds the 32 threads of a warp, and the warp sums are
+    added in order.  (threads, chunk) default to `rmsnorm_sum_layout(K)`."""
     M, K = x_bits.shape
+    if threads is None or chunk is None:
+        threads, chunk = rmsnorm_sum_layout(K)
     x = bf16_bits_to_f32(x_bits)
-    chunks = K // 16
-    sq = (x * x).astype(np.float32).reshape(M, chunks, 16)          # exact: squares of bf16 values fit fp32
+    chunks = K // chunk
+    sq = (x * x).astype(np.float32).reshape(M, chunks, chunk)       # exact: squares of bf16 values fit fp32
     part = np.zeros((M, threads), np.float32)
     for w0 in range(0, chunks, threads):
         n = min(threads, chunks - w0)
-        for e in range(16):
+        for e in range(chunk):
             part[:, :n] = (part[:, :n] + sq[:, w0:w0 + n, e]).astype(np.float32)
     lanes = part.reshape(M, threads // 32, 32)
     idx = np.arange(32)

@@ -43,6 +43,7 @@ SIGNATURES = {
     "tq_dequant_finish_partials": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "tq_tail_gather_small": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "tq_set_gemm_pair_mode": [_I],
+    "tq_set_prologue_mode": [_I],
     "tq_gemm_status": [_P],
 }
 _CHAR_P_RETURNS = {"tq_error_string", "tq_last_cuda_error"}

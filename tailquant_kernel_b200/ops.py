@@ -162,7 +162,7 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
 def _topr_pack(name, A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps):
     _check_cuda(A, "A")
     _check(A.dim() == 2, "A must be [M, K]")
-    _check(A.dtype in (torch.bfloat16, torch.float16), "A must be bf16 (fp16 is not built)")
+    _check(A.dtype in (torch.bfloat16, torch.float16), "A must be bf16 or fp16")
     M, K = A.shape
     R, descending_rank = int(R), int(descending_rank)
     _check_cuda(A_pack, "A_pack", torch.uint8)
@@ -329,6 +329,12 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
 def set_gemm_pair_mode(mode: int) -> None:
     """-1: split_gemm_mma picks its kernel by problem size; 0: one CTA per tile; 1: CTA pairs (256 x 256 tiles)."""
     _lib.check(_lib.load().tq_set_gemm_pair_mode(int(mode)), "set_gemm_pair_mode")
+
+
+def set_prologue_mode(mode: int) -> None:
+    """-1: the prologue kernel specialised for K = 4096 / 12288 / 14336 where it applies; 0: the general kernel only
+    (both give the same bits; a switch for comparisons)."""
+    _lib.check(_lib.load().tq_set_prologue_mode(int(mode)), "set_prologue_mode")
 
 
 def dequant_finish(C, body_scale, w_scale, out, tail=None, bias=None):

@@ -35,9 +35,10 @@ def column_shard(N: int, rank: int, world: int, multiple: int = 64) -> Tuple[int
 
 def gather_columns(y_local, N: int, group=None, multiple: int = 64):
     """The one exchange step of the column-parallel split: every rank holds the [M, n_r] output slab of its
-    channels (`column_shard`) and receives the full [M, N] output.  One all-gather over the process group
-    (NCCL over NVLink on GPUs, gloo on CPU); slabs of unequal width are padded to the widest for the
-    collective and trimmed afterwards."""
+    channels (`column_shard`) and receives the full [M, N] output.  One `all_gather_into_tensor` over the process
+    group (NCCL over NVLink on GPUs, gloo on CPU) into a [world, M, widest] buffer, then ONE strided copy into the
+    [M, N] result when the slabs are equal (N / multiple divisible by the world size: every projection of the
+    benchmarked models), or one copy per rank when a narrower last slab was padded to the widest."""
     import torch
     import torch.distributed as dist
 
@@ -48,15 +49,19 @@ def gather_columns(y_local, N: int, group=None, multiple: int = 64):
     if y_local.shape[1] != shards[rank][1]:
         raise RuntimeError(f"rank {rank} holds {y_local.shape[1]} columns, its shard has {shards[rank][1]}")
     widest = max(c for _, c in shards)
-    send = y_local
-    if send.shape[1] != widest:
+    equal = all(c == widest for _, c in shards)
+    send = y_local.contiguous()
+    if not equal and send.shape[1] != widest:
         send = torch.zeros((M, widest), dtype=y_local.dtype, device=y_local.device)
         send[:, : y_local.shape[1]] = y_local
-    parts = [torch.empty((M, widest), dtype=y_local.dtype, device=y_local.device) for _ in range(world)]
-    dist.all_gather(parts, send.contiguous(), group=group)
+    buf = torch.empty((world, M, widest), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(buf, send, group=group)
     out = torch.empty((M, N), dtype=y_local.dtype, device=y_local.device)
-    for (s0, c), part in zip(shards, parts):
-        out[:, s0:s0 + c] = part[:, :c]
+    if equal:
+        out.view(M, world, widest).copy_(buf.permute(1, 0, 2))
+    else:
+        for r, (s0, c) in enumerate(shards):
+            out[:, s0:s0 + c] = buf[r, :, :c]
     return out
 
 

@@ -115,6 +115,73 @@ def test_prologue_parity(kind, K, M, R, data, pct):
     assert np.array_equal(out.a_pack.cpu().numpy(), ref.a_pack), "packed INT4 codes"
 
 
+FAST_CASES = [
+    # kind, K, R, pct, data: every (rotation, width) that has the specialised prologue kernel
+    (O.HAD_WHT, 4096, 205, 100.0, "outlier"), (O.HAD_WHT, 4096, 0, 100.0, "outlier"), (O.HAD_WHT, 4096, 205, 98.5, "ties"),
+    (O.HAD_KRON12, 12288, 615, 100.0, "outlier"), (O.HAD_BLOCK128, 14336, 717, 100.0, "outlier"),
+    (O.HAD_BLOCK128, 14336, 1434, 100.0, "wide"), (O.HAD_NONE, 4096, 82, 99.477, "col257"),
+    (O.HAD_NONE, 12288, 615, 100.0, "wide"), (O.HAD_NONE, 14336, 144, 100.0, "ties"),
+]
+
+
+@pytest.mark.parametrize("kind,K,R,pct,data", FAST_CASES)
+def test_specialised_prologue_equals_general_kernel(kind, K, R, pct, data):
+    """The two prologue kernels on 300 rows (more rows than resident CTAs per SM x a few SMs, so CTAs loop over
+    rows): every output tensor, including the GEMM's records, is the same bits."""
+    M = 300
+    x = dev_bf16(make_x(M, K, seed=K + R, kind=data))
+    _, dr, _ = O.split_select_params(K, R, pct)
+    outs = []
+    for mode in (0, -1):
+        ops.set_prologue_mode(mode)
+        try:
+            a = ops.split_prologue(x, kind, R, dr, t16=True, t4=True, want_x_rot=True, want_q8=True)
+            torch.cuda.synchronize()
+        finally:
+            ops.set_prologue_mode(-1)
+        outs.append(a)
+    g, f = outs
+    names = ["x_rot", "a_pack", "a_q8", "body_scale", "top_scale"]
+    if R:
+        names += ["tail_idx", "tail_val", "idx32", "top_q", "tail_ptr", "tail_cnt"]
+    for n in names:
+        assert torch.equal(getattr(g, n).view(torch.uint8), getattr(f, n).view(torch.uint8)), n
+    if R:
+        cnt = host_bits(g.tail_cnt).astype(np.int64)
+        valid = np.arange(12).reshape(1, 1, 1, 12) < np.minimum(cnt, 12)[:, :, :, None]
+        assert np.array_equal(g.tail_rec.cpu().numpy()[valid], f.tail_rec.cpu().numpy()[valid]), "slice records"
+
+
+@pytest.mark.parametrize("K,M,R,pct", [(4096, 64, 41, 98.3), (4096, 33, 164, 100.0), (12288, 9, 123, 99.477), (4096, 5, 0, 100.0)])
+def test_topr_pack_fp16_input(K, M, R, pct):
+    """The reference's own input type at its entry points (fp16 rows, tools/fused_threshold_topr_pack_ext_v57.py:
+    246-259; inputs as in tools/bench_topr_select_algos_v38.py:80-83): select on the 15-bit magnitude of the half,
+    scales and codes from the fp16 values."""
+    rng = np.random.default_rng(K + M + R)
+    xh = rng.standard_normal((M, K), dtype=np.float32).astype(np.float16)
+    xh[:, ::257] *= np.float16(8.0)
+    bits = xh.view(np.uint16)
+    _, dr, _ = O.split_select_params(K, R, pct)
+    ref = O.prologue(bits, O.HAD_NONE, R, dr, fmt="fp16")
+    A = torch.from_numpy(xh).cuda()
+    A_pack = torch.empty(M * K // 2, dtype=torch.uint8, device="cuda")
+    bs = torch.empty(M, dtype=torch.float32, device="cuda")
+    ts = torch.empty(M, dtype=torch.float32, device="cuda")
+    tq = torch.empty((M, max(R, 1)), dtype=torch.int8, device="cuda")
+    idx = torch.empty((M, max(R, 1)), dtype=torch.int32, device="cuda")
+    for fn in (ops.fused_topr_pack, ops.threshold_topr_pack):
+        fn(A, R, dr, A_pack, bs, ts, tq, idx, 1e-8)
+        torch.cuda.synchronize()
+        assert np.array_equal(A_pack.cpu().numpy().reshape(M, K // 2), ref.a_pack)
+        assert np.array_equal(bs.cpu().numpy(), ref.body_scale)
+        assert np.array_equal(ts.cpu().numpy(), ref.top_scale)
+        if R:
+            assert np.array_equal(idx.cpu().numpy(), ref.idx)
+            assert np.array_equal(tq.cpu().numpy(), ref.top_q)
+    with pytest.raises(RuntimeError):  # a width the fp16 entry is not built for
+        ops.fused_topr_pack(A[:, :2048].contiguous(), 10, 11, A_pack, bs, ts, tq, idx, 1e-8)
+
+
 def test_prologue_is_deterministic_and_row_independent():
     K, R = 4096, 205
     xb = make_x(300, K, seed=11)
@@ -521,6 +588,85 @@ def test_adapter_calling_conventions():
     ref = x.float() @ W.float().t() + bias
     rel = (y0.float() - ref).norm() / ref.norm()
     assert rel < 0.2
+
+
+def test_adapter_cache_follows_the_weight_object_and_returns_fresh_tensors():
+    """The adapter callable gets the raw weight on every call.  A new weight tensor that the allocator places at the
+    address of a dead one must not hit the dead one's prepared weights, and two calls must not share output storage
+    (the callable stands in for nn.Linear)."""
+    import gc
+    from tailquant_kernel_b200 import SplitLinear, linear
+    M, K, N = 80, 1024, 264
+    x = dev_bf16(O.make_activations(M, K, seed=0, n_outlier=4))
+    linear.clear_cache()
+    W1 = dev_bf16(O.make_weights(N, K, seed=1))
+    y1 = linear.split_linear_forward(x, W1, ratio=0.05)
+    ptr = W1.data_ptr()
+    del W1
+    gc.collect()
+    W2 = dev_bf16(O.make_weights(N, K, seed=2))  # same shape: the caching allocator hands the block out again
+    y2 = linear.split_linear_forward(x, W2, ratio=0.05)
+    assert torch.equal(y2, SplitLinear(W2, ratio=0.05)(x)), "stale prepared weights were used"
+    if W2.data_ptr() == ptr:
+        assert not torch.equal(y1, y2)
+    y3 = linear.split_linear_forward(x, W2, ratio=0.05)
+    assert y3.data_ptr() != y2.data_ptr() and torch.equal(y3, y2)
+    assert len(linear._CACHE) == 1, "the dead weight's entry must be gone"
+
+
+def test_adapter_shares_one_prologue_between_layers_on_the_same_input():
+    """q / k / v (and gate / up) of a model patched module by module call the adapter callable one after the other on
+    the same input tensor: the second and third run on the first one's prologue
+    (tools/bench_prefill_bf16_romeoquarotdense_split_total_v61_sharedprepare.py:221-261), with outputs of their own
+    width, and give the bits of independent layers."""
+    from tailquant_kernel_b200 import SplitLinear, linear
+    M, K = 200, 1024
+    x = dev_bf16(O.make_activations(M, K, seed=3, n_outlier=4))
+    Wq, Wk, Wv = (dev_bf16(O.make_weights(n, K, seed=10 + i)) for i, n in enumerate((512, 136, 136)))
+    linear.clear_cache()
+    calls = []
+    real = linear.SplitLinear.prologue
+
+    def counting(self, x2d):
+        calls.append(self.N)
+        return real(self, x2d)
+
+    linear.SplitLinear.prologue = counting
+    try:
+        ys = [linear.split_linear_forward(x, W, ratio=0.05) for W in (Wq, Wk, Wv)]
+        assert calls == [512], f"prologues run: {calls}"
+        x2 = x.clone()
+        ys2 = [linear.split_linear_forward(x2, W, ratio=0.05) for W in (Wq, Wk, Wv)]
+        assert calls == [512, 512]
+        x2.add_(1.0)  # in-place change: the shared prologue must not be reused
+        linear.split_linear_forward(x2, Wk, ratio=0.05)
+        assert calls == [512, 512, 136]
+    finally:
+        linear.SplitLinear.prologue = real
+    for W, y, yb in zip((Wq, Wk, Wv), ys, ys2):
+        assert tuple(y.shape) == (M, W.shape[0])
+        assert torch.equal(y, SplitLinear(W, ratio=0.05)(x)) and torch.equal(y, yb)
+    # small M (decode kernels) through the same path
+    xs = x[:8].contiguous()
+    ya = [linear.split_linear_forward(xs, W, ratio=0.05) for W in (Wq, Wk)]
+    for W, y in zip((Wq, Wk), ya):
+        assert torch.equal(y, SplitLinear(W, ratio=0.05)(xs))
+
+
+def test_saved_layer_keeps_its_fused_norm_and_epilogue(tmp_path):
+    from tailquant_kernel_b200 import SplitLinear, interleave_gate_up
+    rng = np.random.default_rng(9)
+    K, I, M = 1024, 136, 150
+    wg = torch.from_numpy(rng.standard_normal((I, K)).astype(np.float32) * 0.02).to(torch.bfloat16).cuda()
+    wu = torch.from_numpy(rng.standard_normal((I, K)).astype(np.float32) * 0.02).to(torch.bfloat16).cuda()
+    gamma = torch.from_numpy(1.0 + 0.2 * rng.standard_normal(K).astype(np.float32)).to(torch.bfloat16).cuda()
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32) * 3).to(torch.bfloat16).cuda()
+    lin = SplitLinear(interleave_gate_up(wg, wu), ratio=0.05, epilogue="swiglu", rms_weight=gamma, rms_eps=1e-5)
+    y0 = lin(x).clone()
+    lin.save(tmp_path / "gu.tqw")
+    lin2 = SplitLinear.load(tmp_path / "gu.tqw")
+    assert lin2.epilogue == "swiglu" and lin2.rms_eps == 1e-5 and torch.equal(lin2.rms_weight, gamma)
+    assert torch.equal(lin2(x), y0) and tuple(y0.shape) == (M, I)
 
 
 def test_full_size_properties_qwen3_layer_shapes():
