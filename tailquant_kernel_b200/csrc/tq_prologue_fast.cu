@@ -240,13 +240,17 @@ template <int KIND, int K>
 struct FS {
   static constexpr int NT = K / 64;
   static constexpr bool XBUF = (KIND == TQ_HAD_WHT || KIND == TQ_HAD_KRON12);
+  // K = 4096: the fp32 exchange buffer starts AT the row buffer (the 16-bit row is dead between the first register
+  // pass and the write-back of the rotated row; one barrier after the second pass's loads keeps the two apart)
+  static constexpr bool ALIAS = (KIND == TQ_HAD_WHT);
   static constexpr int ROW_OFF = 0;                        // [K] 16-bit row, [K/64][8 chunks of 16 B], chunk ^= row & 7
-  static constexpr int X_OFF = K * 2;                      // [K] fp32 exchange buffer, rows of 256 B, same swizzle;
-                                                           // after the rotation: [K] u16 list of the row's tail
-                                                           // indices, then [K/64] u32 list position of each half slice
-  static constexpr int LIST_OFF = X_OFF;
-  static constexpr int HST_OFF = X_OFF + K * 2;
-  static constexpr int HIST_OFF = X_OFF + (XBUF ? K * 4 : K * 2 + (K / 64) * 4);
+  static constexpr int X_OFF = ALIAS ? 0 : K * 2;          // [K] fp32 exchange buffer, rows of 256 B, same swizzle
+  // after the rotation: [K] u16 list of the row's tail indices, then [K/64] u32 list position of each half slice
+  static constexpr int LIST_OFF = K * 2;
+  static constexpr int HST_OFF = LIST_OFF + K * 2;
+  static constexpr int AUX_END = HST_OFF + (K / 64) * 4;
+  static constexpr int X_END = XBUF ? X_OFF + K * 4 : 0;
+  static constexpr int HIST_OFF = (AUX_END > X_END ? AUX_END : X_END);
   static constexpr int RED_OFF = HIST_OFF + 1024;          // 16 words: block max / sums
   static constexpr int RES_OFF = RED_OFF + 64;             // 8 words: select result
   static constexpr int SCAN_OFF = RES_OFF + 32;            // 8 words: warp totals of the scan
@@ -254,7 +258,7 @@ struct FS {
   static constexpr int DYN = BAR_OFF + 16 + 1024;          // + alignment slack
 };
 
-constexpr int fast_min_ctas(int K) { return K <= 4096 ? 8 : (K <= 12288 ? 3 : 2); }
+constexpr int fast_min_ctas(int K) { return K <= 4096 ? 10 : (K <= 12288 ? 3 : 2); }
 
 template <int KIND, int K, int DT, bool NORM>
 __global__ void __launch_bounds__(K / 64, fast_min_ctas(K))
@@ -404,6 +408,7 @@ prologue_fast_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrologueP
           sts128(my_row + (((uint32_t)c << 4) ^ my_sw), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
       } else if (KIND == TQ_HAD_WHT) {
         // ---- transpose through the fp32 buffer: element i of thread t -> (row i, column t)
+        if (S::ALIAS) __syncthreads();  // (the buffer overlays the 16-bit row: every thread has read its part)
         {
           const smp wb = xbuf + (tid & 3) * 4;
           const uint32_t ch = (uint32_t)(tid >> 2);
@@ -429,6 +434,7 @@ prologue_fast_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrologueP
             v[2 * c + 1] = pk2(__uint_as_float(q.z), __uint_as_float(q.w));
           }
         }
+        if (S::ALIAS) __syncthreads();  // every thread has its values: the rotated row may overwrite the exchange buffer
         wht64(v);  // strides 64 .. 2048: the thread holds elements 64 j + t
         // ---- normalise, round, park the bf16 row in index order: element 64 j + t -> (row j, position t)
         {
