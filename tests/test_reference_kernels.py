@@ -1,0 +1,150 @@
+"""The reference-compatible (T4) entry points against the reference's OWN CUDA kernels.
+
+The only executable pieces of the reference are its self-contained `load_inline` extensions.  `oracle/make_ref.py`
+builds two of them, unmodified and with the reference's own loader and flags, into the untracked oracle/_ref/:
+`threshold_topr_pack` (tools/fused_threshold_topr_pack_ext_v57.py) and `scale_sparse_epilogue_quad|oct`
+(tools/fused_sparse_epilogue_ext_v58.py).  Both sides get the reference's own input generators.
+
+What must agree, and what may differ: the reference builds with --use_fast_math
+(tools/fused_threshold_topr_pack_ext_v57.py: extra_cuda_cflags), i.e. approximate division and fused multiply-adds,
+while this library evaluates true fp32 divisions in a fixed order.  So
+  * tail index SETS (integer keys, lowest index wins a tie) must be identical, row by row;
+  * scales may differ by at most 2 fp32 ulps;
+  * INT4 codes must be equal except where x / scale lies within 1e-4 of a rounding boundary, never by more than one
+    step, and on fewer than one element in a thousand;
+  * fp16 outputs of the epilogue must be within one fp16 ulp, and equal on more than 99.9 % of the elements.
+The mismatch counts are printed.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from oracle import make_ref  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+ops = None
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _load():
+    global ops
+    if not make_ref.built():
+        pytest.skip("oracle/_ref/ is not built (python oracle/make_ref.py --reference <tree>)")
+    from tailquant_kernel_b200 import ops as _ops
+    ops = _ops
+    yield
+
+
+def ulps32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    return np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))
+
+
+def unpack_codes(p: np.ndarray) -> np.ndarray:
+    lo = (p & 0xF).astype(np.int8)
+    hi = (p >> 4).astype(np.int8)
+    out = np.empty((p.shape[0], p.shape[1] * 2), dtype=np.int8)
+    out[:, 0::2] = lo
+    out[:, 1::2] = hi
+    return np.where(out >= 8, out - 16, out).astype(np.int8)
+
+
+@pytest.mark.parametrize("K,M,R,pct,pattern", [
+    # tools/bench_topr_select_algos_v38.py:80-83: randn(2048, 4096) fp16, R in {41, 82, 164}, percentiles 98.3 / 99.477
+    (4096, 2048, 41, 98.3, "randn"), (4096, 2048, 82, 99.477, "randn"), (4096, 2048, 164, 98.3, "randn"),
+    # tools/compare_single_matrix_fake_vs_kernel_quant_l2_v1.py:155-157: every 257th column x8; percentile 100
+    (4096, 128, 21, 100.0, "col257"), (12288, 64, 63, 100.0, "col257"),
+])
+def test_threshold_topr_pack_against_the_reference_kernel(K, M, R, pct, pattern):
+    ref = make_ref.load("threshold_topr_pack_v57_ext")
+    torch.manual_seed(0)
+    A = torch.randn((M, K), device="cuda", dtype=torch.float32)
+    if pattern == "col257":
+        A[:, ::257] *= 8.0
+    A = A.to(torch.float16).contiguous()
+    _, dr, _ = ops.split_select_params(K, R, pct)
+
+    def run(fn):
+        A_pack = torch.empty(M * K // 2, dtype=torch.uint8, device="cuda")
+        bs = torch.empty(M, dtype=torch.float32, device="cuda")
+        ts = torch.empty(M, dtype=torch.float32, device="cuda")
+        tq = torch.empty((M, R), dtype=torch.int8, device="cuda")
+        idx = torch.empty((M, R), dtype=torch.int32, device="cuda")
+        fn(A, R, dr, A_pack, bs, ts, tq, idx, 1e-8)
+        torch.cuda.synchronize()
+        return (A_pack.cpu().numpy().reshape(M, K // 2), bs.cpu().numpy(), ts.cpu().numpy(), tq.cpu().numpy(),
+                idx.cpu().numpy())
+
+    rp, rbs, rts, rtq, ridx = run(ref.threshold_topr_pack)
+    op, obs, ots, otq, oidx = run(ops.threshold_topr_pack)
+    # index sets (the reference emits the keys above the threshold, then the ties, each ascending; we emit ascending)
+    order = np.argsort(ridx, axis=1, kind="stable")
+    assert np.array_equal(np.take_along_axis(ridx, order, axis=1), oidx), "tail index sets differ"
+    assert ulps32(rbs, obs).max() <= 2 and ulps32(rts, ots).max() <= 2, "scales differ by more than 2 ulp"
+    xf = A.float().cpu().numpy().astype(np.float64)
+
+    def check_codes(got, want, scale, what):
+        bad = got != want
+        n = int(bad.sum())
+        if n:
+            assert np.abs(got.astype(np.int32) - want.astype(np.int32))[bad].max() <= 1, f"{what}: a code is off by more than one"
+            t = (np.broadcast_to(xf_sel, got.shape)[bad] / np.broadcast_to(scale.astype(np.float64).reshape(-1, 1), got.shape)[bad])
+            frac = np.abs(np.abs(t - np.floor(t)) - 0.5)
+            clamp_edge = (np.abs(t) > 7.4)
+            assert np.all((frac < 1e-4) | clamp_edge), f"{what}: codes differ away from a rounding boundary"
+        assert n <= max(1, got.size // 1000), f"{what}: {n} of {got.size} codes differ"
+        return n
+
+    xf_sel = xf
+    n_body = check_codes(unpack_codes(op), unpack_codes(rp), obs, "body codes")
+    xf_sel = np.take_along_axis(xf, oidx.astype(np.int64), axis=1)
+    n_tail = check_codes(otq, np.take_along_axis(rtq, order, axis=1), ots, "tail codes")
+    print(f"threshold_topr_pack K={K} M={M} R={R}: scales max {max(ulps32(rbs, obs).max(), ulps32(rts, ots).max())} ulp, "
+          f"{n_body} body and {n_tail} tail codes differ (rounding boundaries under --use_fast_math)")
+
+
+@pytest.mark.parametrize("M,N,K,R", [(128, 4096, 4096, 30), (128, 4096, 4096, 21), (2048, 4096, 4096, 63), (128, 1032, 12288, 30)])
+def test_scale_sparse_epilogue_against_the_reference_kernel(M, N, K, R):
+    """Generators of tools/smoke_quarot_split_fused_epilogue_v1.py:46-64 and the shapes / R values of
+    tools/smoke_split_kernel_optimization_5points_v1.py:38-39."""
+    ref = make_ref.load("fused_sparse_epilogue_v58_ext")
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    A_q_full = torch.randint(-8, 8, (M, K), dtype=torch.int8, device=dev)
+    B_q = torch.randint(-8, 8, (N, K), dtype=torch.int8, device=dev)
+    idx = torch.stack([torch.randperm(K, device=dev)[:R] for _ in range(M)]).to(torch.int32).contiguous()
+    top_q = torch.gather(A_q_full, 1, idx.to(torch.int64)).contiguous()
+    A_body = A_q_full.clone()
+    A_body.scatter_(1, idx.to(torch.int64), 0)
+
+    def pack(q):  # element 2i -> low nibble
+        u = (q.to(torch.int16) & 0xF).to(torch.uint8)
+        return (u[:, 0::2] | (u[:, 1::2] << 4)).contiguous()
+
+    B_row = pack(B_q.t().contiguous())
+    bs = torch.empty(M, dtype=torch.float32, device=dev).uniform_(0.001, 0.02)
+    ts = torch.empty(M, dtype=torch.float32, device=dev).uniform_(0.001, 0.02)
+    ws = torch.empty(N, dtype=torch.float32, device=dev).uniform_(0.001, 0.02)
+    C = ops.matmul(pack(A_body), pack(B_q))  # the dense INT4 x INT4 product of the same data
+    assert torch.equal(C, torch._int_mm(A_body, B_q.t().contiguous())) if M > 16 else True
+    for name in ("scale_sparse_epilogue_quad", "scale_sparse_epilogue_oct"):
+        out_ref = torch.empty((M, N), dtype=torch.float16, device=dev)
+        out_our = torch.empty((M, N), dtype=torch.float16, device=dev)
+        getattr(ref, name)(C, bs, top_q, idx, B_row, ts, ws, out_ref, K)
+        getattr(ops, name)(C, bs, top_q, idx, B_row, ts, ws, out_our, K)
+        torch.cuda.synchronize()
+        a = out_ref.view(torch.int16).cpu().numpy().astype(np.int32)
+        b = out_our.view(torch.int16).cpu().numpy().astype(np.int32)
+        diff = a != b
+        n = int(diff.sum())
+        if n:  # adjacent fp16 values (sign-magnitude bit patterns: neighbours differ by one)
+            assert np.abs(a - b)[diff].max() <= 1, f"{name}: an output is more than one fp16 ulp away"
+        assert n <= a.size // 1000, f"{name}: {n} of {a.size} outputs differ"
+        print(f"{name} M={M} N={N} K={K} R={R}: {n} of {a.size} fp16 outputs differ by one ulp (fused multiply-add)")
