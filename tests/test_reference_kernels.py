@@ -14,6 +14,15 @@ while this library evaluates true fp32 divisions in a fixed order.  So
     step, and on fewer than one element in a thousand;
   * fp16 outputs of the epilogue must be within one fp16 ulp, and equal on more than 99.9 % of the elements.
 The mismatch counts are printed.
+
+One defect of the reference kernel has to be stepped around.  Its radix select keeps its result in a `__shared__`
+variable that every thread reads AFTER the function's last barrier (`return s_prefix`,
+tools/fused_threshold_topr_pack_ext_v57.py:93) while thread 0, already in the next of the three back-to-back calls
+(:125-127), resets it to 0 (:55-58) -- a shared-memory race.  On B200 a few percent of the rows lose it: whole warps
+then see a tail threshold of 0 and emit runs of consecutive indices.  Such rows are recognisable from the reference's
+output alone (the emitted indices are not a top-R set of the row: some emitted key is smaller than some key left
+out); they are counted, reported and left out of the comparison, which then covers every row the reference computed
+according to its own definition.  (Scales are written by thread 0 from its own reads and are compared on all rows.)
 """
 import os
 import sys
@@ -84,9 +93,19 @@ def test_threshold_topr_pack_against_the_reference_kernel(K, M, R, pct, pattern)
 
     rp, rbs, rts, rtq, ridx = run(ref.threshold_topr_pack)
     op, obs, ots, otq, oidx = run(ops.threshold_topr_pack)
+    # rows on which the reference kernel lost its shared-memory race: its own output is not a top-R set there
+    keys = (A.view(torch.int16).cpu().numpy().view(np.uint16) & 0x7FFF).astype(np.int32)
+    sel = np.zeros((M, K), dtype=bool)
+    np.put_along_axis(sel, np.clip(ridx, 0, K - 1).astype(np.int64), True, axis=1)
+    distinct = sel.sum(axis=1) == R
+    min_in = np.where(sel, keys, 1 << 20).min(axis=1)
+    max_out = np.where(sel, -1, keys).max(axis=1)
+    good = distinct & (min_in >= max_out)
+    n_raced = int((~good).sum())
+    assert n_raced <= M // 4, f"the reference kernel's output is not a top-R set on {n_raced} of {M} rows"
     # index sets (the reference emits the keys above the threshold, then the ties, each ascending; we emit ascending)
     order = np.argsort(ridx, axis=1, kind="stable")
-    assert np.array_equal(np.take_along_axis(ridx, order, axis=1), oidx), "tail index sets differ"
+    assert np.array_equal(np.take_along_axis(ridx, order, axis=1)[good], oidx[good]), "tail index sets differ"
     assert ulps32(rbs, obs).max() <= 2 and ulps32(rts, ots).max() <= 2, "scales differ by more than 2 ulp"
     xf = A.float().cpu().numpy().astype(np.float64)
 
@@ -95,25 +114,34 @@ def test_threshold_topr_pack_against_the_reference_kernel(K, M, R, pct, pattern)
         n = int(bad.sum())
         if n:
             assert np.abs(got.astype(np.int32) - want.astype(np.int32))[bad].max() <= 1, f"{what}: a code is off by more than one"
-            t = (np.broadcast_to(xf_sel, got.shape)[bad] / np.broadcast_to(scale.astype(np.float64).reshape(-1, 1), got.shape)[bad])
+            t = xf_sel[bad] / np.broadcast_to(scale.astype(np.float64).reshape(-1, 1), got.shape)[bad]
             frac = np.abs(np.abs(t - np.floor(t)) - 0.5)
             clamp_edge = (np.abs(t) > 7.4)
             assert np.all((frac < 1e-4) | clamp_edge), f"{what}: codes differ away from a rounding boundary"
         assert n <= max(1, got.size // 1000), f"{what}: {n} of {got.size} codes differ"
         return n
 
-    xf_sel = xf
-    n_body = check_codes(unpack_codes(op), unpack_codes(rp), obs, "body codes")
-    xf_sel = np.take_along_axis(xf, oidx.astype(np.int64), axis=1)
-    n_tail = check_codes(otq, np.take_along_axis(rtq, order, axis=1), ots, "tail codes")
-    print(f"threshold_topr_pack K={K} M={M} R={R}: scales max {max(ulps32(rbs, obs).max(), ulps32(rts, ots).max())} ulp, "
+    xf_sel = xf[good]
+    n_body = check_codes(unpack_codes(op)[good], unpack_codes(rp)[good], obs[good], "body codes")
+    xf_sel = np.take_along_axis(xf, oidx.astype(np.int64), axis=1)[good]
+    n_tail = check_codes(otq[good], np.take_along_axis(rtq, order, axis=1)[good], ots[good], "tail codes")
+    print(f"threshold_topr_pack K={K} M={M} R={R}: {int(good.sum())} rows compared ({n_raced} rows where the reference's "
+          f"own output is not a top-R set), scales max {max(ulps32(rbs, obs).max(), ulps32(rts, ots).max())} ulp, "
           f"{n_body} body and {n_tail} tail codes differ (rounding boundaries under --use_fast_math)")
 
 
-@pytest.mark.parametrize("M,N,K,R", [(128, 4096, 4096, 30), (128, 4096, 4096, 21), (2048, 4096, 4096, 63), (128, 1032, 12288, 30)])
+@pytest.mark.parametrize("M,N,K,R", [(128, 4096, 4096, 30), (128, 4096, 4096, 21), (2048, 4096, 4096, 63),
+                                     (256, 12288, 4096, 30), (256, 4096, 12288, 21)])
 def test_scale_sparse_epilogue_against_the_reference_kernel(M, N, K, R):
     """Generators of tools/smoke_quarot_split_fused_epilogue_v1.py:46-64 and the shapes / R values of
-    tools/smoke_split_kernel_optimization_5points_v1.py:38-39."""
+    tools/smoke_split_kernel_optimization_5points_v1.py:38-39.
+
+    Only N that are multiples of 1024 (128 threads x 8 columns) go to the reference kernel, as in all of its own
+    smokes: its threads beyond N return BEFORE the block stages idx / top_q in shared memory
+    (tools/fused_sparse_epilogue_ext_v58.py:41-53), so in a partly filled last block the staged lists are
+    incomplete and the kernel reads weight rows at uninitialised indices.  (This library's kernels take any N % 8 == 0;
+    that is covered against the CPU oracle in test_gpu_parity.py.)"""
+    assert N % 1024 == 0
     ref = make_ref.load("fused_sparse_epilogue_v58_ext")
     torch.manual_seed(0)
     dev = torch.device("cuda")
