@@ -390,23 +390,31 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       // (The record arrays cover 2 * ceil(M / 256) row tiles, and rows at or beyond M have zero counts: no bounds
       // checks here.)
       size_t fhs = my_tiles > 0 ? ((size_t)(2 * tile_mt(0) + (int)rank) * kbt) * 2 + half : 0;
+      // The count of a half slice is requested one fetch ahead of its record (npre), so that the record's third
+      // 128-bit word -- entries 8..11, needed by one row in two hundred -- is only loaded where it exists.
+      auto load_cnt = [&](size_t hs) -> int {
+        uint32_t n16;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + hs * 128 + brow));
+        return (int)n16;
+      };
+      int npre = my_tiles > 0 ? load_cnt(fhs) : 0;
       auto fetch = [&](uint32_t(&r)[C], int& n) {
         if (fi < my_tiles) {
           const uint4* recb = reinterpret_cast<const uint4*>(p.rec + (fhs * 128 + brow) * C);
-          uint32_t n16;
-          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(n16) : "l"(p.cnt + fhs * 128 + brow));
-          n = (int)n16;
+          n = npre;
 #pragma unroll
           for (int j = 0; j < C / 4; ++j)  // the row's record: C words in a row, a warp reads 32 C contiguous words
-            asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(r[4 * j]), "=r"(r[4 * j + 1]), "=r"(r[4 * j + 2]), "=r"(r[4 * j + 3])
-                         : "l"(recb + j));
+            if (j < 2 || n > 4 * j)
+              asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(r[4 * j]), "=r"(r[4 * j + 1]), "=r"(r[4 * j + 2]), "=r"(r[4 * j + 3])
+                           : "l"(recb + j));
           fhs += 2;
           if (++fkb == kbt) {  // next tile of the pair
             fkb = 0;
             ++fi;
             if (fi < my_tiles) fhs = ((size_t)(2 * tile_mt(fi) + (int)rank) * kbt) * 2 + half;
           }
+          if (fi < my_tiles) npre = load_cnt(fhs);
         } else {
           n = 0;
         }
