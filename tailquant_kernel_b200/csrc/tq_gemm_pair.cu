@@ -58,7 +58,7 @@ struct PS {
   static constexpr int STAGE = P_BH * (P_BK / 2);
   static constexpr int STAGE_OFF = SU * SLOT;
   static constexpr int BAR_OFF = STAGE_OFF + SP * STAGE;
-  static constexpr int NUM_BARS = 2 * SP + 2 * SU + 2;
+  static constexpr int NUM_BARS = 2 * SP + 2 * SU + 4;  // + accumulator full / empty, two buffers each
   static constexpr int DYN = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
 };
 static_assert(PS::DYN <= 232448, "shared memory of the pair kernel");
@@ -84,8 +84,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
   auto empty_p = [&](int s) { return bars + 8u * (S::SP + s); };
   auto full_u = [&](int s) { return bars + 8u * (2 * S::SP + s); };
   auto empty_u = [&](int s) { return bars + 8u * (2 * S::SP + S::SU + s); };
-  const uint32_t acc_full = bars + 8u * (2 * S::SP + 2 * S::SU);
-  const uint32_t acc_empty = acc_full + 8u;
+  auto acc_full = [&](int b) { return bars + 8u * (2 * S::SP + 2 * S::SU + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * S::SP + 2 * S::SU + 2 + b); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + S::BAR_OFF + S::NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + S::BAR_OFF + S::NUM_BARS * 8 + 4);
 
@@ -114,8 +114,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       mbar_init(full_u(s), 8 + 1);  // four warps of each CTA + the leader producer's expect_tx (leader's copy is used)
       mbar_init(empty_u(s), 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 2 * (4 + P_BUILD_WARPS));  // the epilogue warps of both CTAs (leader's copy is used)
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      // the epilogue warps of both CTAs (leader's copy is used): all twelve with a tail, warps 10..13 without
+      mbar_init(acc_empty(b), p.has_tail ? 2 * (4 + P_BUILD_WARPS) : 2 * 4);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -137,8 +140,14 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
 
   // Epilogue share of one warp (2..13) for local tile i: column chunks [c_lo, c_hi) of 32 channels each, rows of
   // the warp's tensor-memory lane quadrant.  y = bf16((float(acc) * s_x) * s_w + tail + bias).
+  // Accumulator buffers: with a tail the int32 and the fp32 accumulator fill the tensor memory (one set; a tile's
+  // MMAs wait for the previous epilogue).  Without a tail the second half holds a second int32 accumulator: tile
+  // i uses buffer i & 1, and its epilogue (warps 10..13) runs under the next tile's main loop.
+  auto acc_buf = [&](int i) { return has_tail ? 0 : (i & 1); };
+  auto acc_use = [&](int i) { return has_tail ? i : (i >> 1); };
   auto epilogue = [&](int i, int c_lo, int c_hi) -> bool {
-    if (!TQ_WAIT(6, mbar_wait(acc_full, (uint32_t)(i & 1), abort_flag, 0x40000u))) return false;
+    const int ab = acc_buf(i);
+    if (!TQ_WAIT(6, mbar_wait(acc_full(ab), (uint32_t)(acc_use(i) & 1), abort_flag, 0x40000u))) return false;
     tc_fence_after();
     const int mt = tile_mt(i), nt = tile_nt(i);
     const int quad = warp & 3;
@@ -146,7 +155,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
     const bool row_ok = row < p.M;
     const float sx = row_ok ? p.sx[row] : 0.0f;
     const size_t rowoff = (size_t)row * p.N;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * BN);
 #pragma unroll 1
     for (int c = c_lo; c < c_hi; ++c) {
       const int c0 = c * 32;
@@ -209,12 +218,13 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive_cluster(lead(acc_empty));
+    if (lane == 0) mbar_arrive_cluster(lead(acc_empty(ab)));
     return true;
   };
   // the eight 32-channel chunks of a tile are split 3 / 3 / 2 over the three warps of a lane quadrant
+  // (without a tail warps 10..13 take all eight chunks and the others none)
   const int ethird = (warp - 2) >> 2;
-  const int c_lo = ethird * 3, c_hi = ethird == 2 ? 8 : ethird * 3 + 3;
+  const int c_lo = has_tail ? ethird * 3 : 0, c_hi = has_tail ? (ethird == 2 ? 8 : ethird * 3 + 3) : 8;
   bool ok = true;
   int epi_done = 0;  // tiles whose epilogue share this warp has done
   auto catch_up = [&](int upto) {
@@ -315,7 +325,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
       int q = 0;
       bool ok = true;
       for (int i = 0; ok && i < my_tiles; ++i) {
-        if (!(ok = TQ_WAIT(3, mbar_wait(acc_empty, (uint32_t)(i & 1) ^ 1u, abort_flag, 0x8000u)))) break;
+        const int ab = acc_buf(i);
+        const uint32_t acc_tmem = tmem_base + (uint32_t)(ab * BN);
+        if (!(ok = TQ_WAIT(3, mbar_wait(acc_empty(ab), (uint32_t)(acc_use(i) & 1) ^ 1u, abort_flag, 0x8000u)))) break;
         tc_fence_after();
         for (int kb = 0; kb < kbt && ok; ++kb) {
           {
@@ -327,7 +339,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
             const uint32_t a_addr = base + s * S::SLOT, b_addr = a_addr + S::B_OFF;
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              umma_i8_pair(tmem_base, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_i8,
+              umma_i8_pair(acc_tmem, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), idesc_i8,
                       (kb > 0 || k > 0) ? 1u : 0u);
             umma_commit_pair(empty_u(s));
             TQ_TRACE(0, q, 2);
@@ -352,7 +364,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
           }
         }
         if (!ok) break;
-        umma_commit_pair(acc_full);
+        umma_commit_pair(acc_full(ab));
       }
     }
   } else if (warp < 6) {
@@ -366,9 +378,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
     for (int g = 0; g < G && ok; g += step) {
       if (!(ok = widen_one(g, etid))) break;
       const int i = g / kbt, kb = g - i * kbt;
-      if (kb >= look - 1 || kb + step >= kbt) catch_up(i);  // (second case: this group's last slice of the tile)
+      if (has_tail && (kb >= look - 1 || kb + step >= kbt)) catch_up(i);  // (second case: this group's last slice of the tile)
     }
-    catch_up(my_tiles);
+    if (has_tail) catch_up(my_tiles);
   } else {
     // ------------------------------------------------------------------ tail builders (+ epilogue share)
     // 256 threads = 128 rows x the two 64-wide halves of a K slice: each builds its row of the zero-filled
@@ -502,11 +514,10 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
         const int wtid = threadIdx.x - 6 * 32;
         for (int g = 1; g < G && ok; g += 2) {
           if (!(ok = widen_one(g, wtid))) break;
-          const int i = g / kbt, kb = g - i * kbt;
-          if (kb >= look - 1 || kb + 2 >= kbt) catch_up(i);
         }
+      } else {
+        catch_up(my_tiles);  // warps 10..13: the epilogues, each under the next tile's main loop
       }
-      catch_up(my_tiles);
     }
   }
 
