@@ -643,15 +643,22 @@ def run_extra(args) -> None:
                 t_all = graph_ms_of(lambda: lin.forward(x))
                 # the weight stream is timed with the packed weights rotating through > 300 MB of copies inside
                 # one graph, so that every launch reads them from HBM and not from the 126 MB L2
+                tc = M >= 32 and N >= 6144  # the layer's dispatch: tcgen05 split-K GEMM from 32 rows on the wide projections
+                part = torch.empty((_ops.gemv_plan(M, N, K), M, N), dtype=torch.int32, device=dev)
+
                 def all_copies():
                     for b in b_copies:
-                        _ops.gemv_partials(ws.pro.a_pack, b, ws.acc)
+                        if tc:
+                            _ops.matmul_splitk(ws.pro.a_pack, b, part[0], lin._pick_split_k(M))
+                        else:
+                            _ops.gemv_partials(ws.pro.a_pack, b, part)
                 t_gemm = graph_ms_of(all_copies) / len(b_copies)
                 t_pro = graph_ms_of(lambda: lin.prologue(x))
                 t_tail = graph_ms_of(lambda: _ops.tail_gather_small(ws.pro.tail_idx, ws.pro.tail_val, lin.w.w_t, ws.tail, lin.R))
                 wbytes = K * N / 2
                 print(json.dumps({"workload": "decode", "linear": name, "M": M, "K": K, "N": N, "R": lin.R,
                                   "linear_ms": t_all, "splitk_gemm_ms": t_gemm,
+                                  "dense_kernel": "tcgen05 split-K GEMM (int32 atomics)" if tc else "weight-streaming GEMV (mma.sync s8), partial sums per K range",
                                   "prologue_ms": t_pro, "tail_gather_ms": t_tail,
                                   "timing": "CUDA graph replay; splitk_gemm_ms = mean launch of the partial-sum GEMV over %d weight copies "
                                             "(HBM-resident), the other figures with L2-warm operands" % len(b_copies),

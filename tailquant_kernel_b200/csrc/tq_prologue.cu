@@ -653,12 +653,22 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
   p.rms_eps = rms_eps;
   // the kernel specialised for the benchmarked widths first (same outputs bit for bit); everything else, and
   // everything when tq_set_prologue_mode(0) asked for it, takes the general kernel
-  if (g_prologue_mode != 0) {
+  // (A handful of rows -- decode -- is a latency problem, not a throughput one: the general kernel puts 256 threads
+  // on a row and finishes a single 4096-wide row about 2 us earlier (a 12288-wide one 4 us later), so it keeps those
+  // calls up to K = 8192 when it can serve them.  With
+  // the fused RMSNorm the specialised kernel always runs: the two sum their squares in different orders, and a
+  // row's result must not depend on how many rows came with it.)
+  const bool few_rows = M <= 64 && K <= 8192 && !gamma && dtype == TQ_BF16;
+  if (g_prologue_mode != 0 && !few_rows) {
     const int rc = run_prologue_fast(had_kind, K, dtype, p, st);
     if (rc != TQ_ERR_UNSUPPORTED) return rc;
   }
   if (dtype != TQ_BF16) return TQ_ERR_UNSUPPORTED;
-  return dispatch(had_kind, K, p, st);
+  {
+    const int rc = dispatch(had_kind, K, p, st);
+    if (rc != TQ_ERR_UNSUPPORTED || g_prologue_mode == 0 || !few_rows) return rc;
+  }
+  return run_prologue_fast(had_kind, K, dtype, p, st);
 }
 
 }  // namespace tq

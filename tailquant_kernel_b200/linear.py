@@ -194,6 +194,12 @@ class SplitLinear:
                                                   M <= self.small_m, self.N_out, with_pro=False)
         return own
 
+    def _pick_split_k(self, M: int) -> int:
+        if self.split_k > 0:
+            return self.split_k
+        tiles = ((M + 127) // 128) * ((self.N + 127) // 128)
+        return max(1, min(self.K // 128, (148 + tiles - 1) // tiles))
+
     def prepare_decode(self) -> None:
         """Builds the [K, N] transpose of the rotated weights that the small-M tail reads, ahead of the first small-M
         forward (which otherwise builds it: an allocation inside that call)."""
@@ -218,10 +224,19 @@ class SplitLinear:
             return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, own.out, w_rot=w.w_rot, pro=pro,
                                       R=self.R, bias=w.bias, act=self.epilogue)
         if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
+            # 32 rows and more on the wide projections: the tcgen05 split-K GEMM (int32 atomics into one slab) is
+            # ahead of the mma.sync GEMV there (measured 34 against 43 us at M = 64 on gate_up)
+            tc = M >= 32 and self.N >= 6144
             if own.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
-                splits = ops.gemv_plan(M, self.N, self.K)
+                splits = 1 if tc else ops.gemv_plan(M, self.N, self.K)
                 own.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=own.out.device)
             self.prepare_decode()
+
+            def dense():
+                if tc:
+                    ops.matmul_splitk(pro.a_pack, w.b_col, own.acc[0], self._pick_split_k(M))
+                else:
+                    ops.gemv_partials(pro.a_pack, w.b_col, own.acc)
             if self.R:
                 if own.tail is None:
                     own.tail = torch.empty((M, self.N), dtype=torch.float32, device=own.out.device)
@@ -234,10 +249,10 @@ class SplitLinear:
                 with torch.cuda.stream(side):
                     ops.tail_gather_small(pro.tail_idx, pro.tail_val, w.w_t, own.tail, self.R)
                     own.ev_join.record(side)
-                ops.gemv_partials(pro.a_pack, w.b_col, own.acc)
+                dense()
                 cur.wait_event(own.ev_join)
             else:
-                ops.gemv_partials(pro.a_pack, w.b_col, own.acc)
+                dense()
             ops.dequant_finish_partials(own.acc, pro.body_scale, w.w_scale, own.out, tail=own.tail, bias=w.bias,
                                         act=self.epilogue)
             return own.out
