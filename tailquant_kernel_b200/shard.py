@@ -54,8 +54,9 @@ def gather_columns(y_local, N: int, group=None, multiple: int = 64):
     if not equal and send.shape[1] != widest:
         send = torch.zeros((M, widest), dtype=y_local.dtype, device=y_local.device)
         send[:, : y_local.shape[1]] = y_local
-    buf = torch.empty((world, M, widest), dtype=y_local.dtype, device=y_local.device)
-    dist.all_gather_into_tensor(buf, send, group=group)
+    flat = torch.empty((world * M, widest), dtype=y_local.dtype, device=y_local.device)  # rank-major concatenation
+    dist.all_gather_into_tensor(flat, send, group=group)
+    buf = flat.view(world, M, widest)
     out = torch.empty((M, N), dtype=y_local.dtype, device=y_local.device)
     if equal:
         out.view(M, world, widest).copy_(buf.permute(1, 0, 2))
