@@ -29,8 +29,6 @@
 // Reference behaviour covered: GEMM + dequant + sparse correction in one kernel, i.e. what the reference
 // prototypes in tools/quarot_split_fused_epilogue_ext_v1.py:283-432 and
 // tools/qfactory_split_fused_epilogue_v1.py:153-233 (there with an INT4 tail and R fixed at compile time).
-#include <cstdlib>
-
 #include "tq_common.cuh"
 #include "tq_ptx.cuh"
 
@@ -527,11 +525,8 @@ int launch_split_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_ro
 }  // namespace tq
 
 namespace tq {
-// -1 = choose by shape, 0 = one-CTA kernel, 1 = CTA-pair kernel (initial value from TQ_GEMM_PAIR)
-static int g_gemm_pair_mode = [] {
-  const char* e = getenv("TQ_GEMM_PAIR");
-  return e ? atoi(e) : -1;
-}();
+// -1 = choose by shape, 0 = one-CTA kernel, 1 = CTA-pair kernel (set by tq_set_gemm_pair_mode only)
+static int g_gemm_pair_mode = -1;
 int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
                   const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
                   const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
@@ -592,7 +587,7 @@ static int run_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const
     // traffic per CTA), from timings over M = 256..8192 on the Qwen3-8B and Llama-3-8B layer shapes: the pair
     // kernel is 1.7-2x faster without a tail and 10-40 % faster with one, except for problems of at most 74
     // one-CTA tiles (half a wave), where a tile's latency decides and the one-CTA kernel is 7-12 % ahead.
-    // TQ_GEMM_PAIR=0 / 1 or tq_set_gemm_pair_mode() force one of them.
+    // tq_set_gemm_pair_mode(0 / 1) forces one of them.
     const long tiles_single = (long)((M + 127) / 128) * ((N + 255) / 256);
     const bool pair = g_gemm_pair_mode == 1 || (g_gemm_pair_mode < 0 && (R == 0 || tiles_single > 74));
     if (pair)
