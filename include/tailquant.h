@@ -80,6 +80,10 @@ const char* tq_last_cuda_error(void);
  *   tail_cnt     [2 ceil(M/256)][K/64][128] u16 entries per (row, half slice) (with tail_rec); the rows that
  *                pad M to a multiple of 256 are written as 0 (both arrays cover them: the CTA-pair GEMM
  *                works on 256-row tiles and does not check rows)
+ *   tail_dense   [M,K] bf16: the rotated row with every element outside the tail set to zero, written when
+ *                R > 0 -- tq_split_gemm_mma loads 32 x 64 blocks of it as operand rows where a row has more
+ *                than TQ_TAIL_REC_CAP entries in a half slice (block-diagonal rotations with outlier channels
+ *                concentrate the tail in a few 128-blocks); may be NULL
  *   idx32        [M,R] i32 the same indices                          (T4; may be NULL)
  *   top_q        [M,R] i8  clamp(rint(x / top_scale), -8, 7)         (T4; may be NULL)
  *   x_rot        [M,K] bf16 rotated activations                      (debug / weight prep; may be NULL)
@@ -87,8 +91,8 @@ const char* tq_last_cuda_error(void);
 int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank, float eps,
                       uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale,
                       uint16_t* tail_idx16, void* tail_val, int tail_ld, uint16_t* tail_ptr, int ptr_ld,
-                      uint32_t* tail_rec, uint16_t* tail_cnt, int32_t* idx32, int8_t* top_q, void* x_rot,
-                      void* stream);
+                      uint32_t* tail_rec, uint16_t* tail_cnt, void* tail_dense, int32_t* idx32, int8_t* top_q,
+                      void* x_rot, void* stream);
 
 /* The same prologue with an RMSNorm fused in front of the rotation (the reference runs the norm as a separate
  * PyTorch module before the linear: tools/bench_layer_async_schedule_v22.py:237,249 -- `layer.input_layernorm`,
@@ -101,8 +105,8 @@ int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int desc
 int tq_split_prologue_rmsnorm(const void* x, const void* gamma, float rms_eps, int M, int K, int had_kind, int R,
                               int descending_rank, float eps, uint8_t* a_pack, int8_t* a_q8, float* body_scale,
                               float* top_scale, uint16_t* tail_idx16, void* tail_val, int tail_ld,
-                              uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt, void* x_rot,
-                              void* stream);
+                              uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt,
+                              void* tail_dense, void* x_rot, void* stream);
 
 /* Reference-signature select+pack on an already rotated matrix (T4 outputs):
  * fused_topr_pack(A, R, descending_rank, A_pack, body_scale, top_scale, top_q, idx, eps)
@@ -166,11 +170,14 @@ int tq_split_gemm_fused(const uint8_t* a_pack, const float* body_scale, const ui
  * prototypes (tools/quarot_split_fused_epilogue_ext_v1.py:283-432).
  *   a_q8      [M,K] i8 from tq_split_prologue       w_rot  [N,K] bf16 from tq_prepare_weight (R > 0)
  *   tail_ptr, tail_rec, tail_cnt  from tq_split_prologue (R > 0)
+ *   tail_dense  optional [M,K] bf16 from tq_split_prologue: with it, the 32-row blocks of a half slice in which a
+ *               row has more than TQ_TAIL_REC_CAP entries are loaded from it by TMA (CTA-pair kernel); without
+ *               it those rows are completed from tail_idx16 / tail_val.  Same results either way.
  *   dbg_acc   optional [M,N] i32: accumulators      dbg_tail  optional [M,N] f32: tail sums */
 int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                       const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
                       const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
-                      const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
+                      const uint32_t* tail_rec, const uint16_t* tail_cnt, const void* tail_dense, int R,
                       const float* bias, void* out_bf16,
                       int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream);
 
@@ -183,7 +190,7 @@ int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t
 int tq_split_gemm_mma_swiglu(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                              const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
                              const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
-                             const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
+                             const uint32_t* tail_rec, const uint16_t* tail_cnt, const void* tail_dense, int R,
                              const float* bias, void* out_bf16, int M, int N, int K, void* stream);
 
 /* tq_split_gemm_mma has two kernels: one CTA per 128 x 256 tile, and CTA pairs on 256 x 256 tiles

@@ -21,11 +21,11 @@ SIGNATURES = {
     "tq_version": [],
     "tq_error_string": [_I],
     "tq_last_cuda_error": [],
-    "tq_split_prologue": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
-    # x, gamma, rms_eps, M, K, had, R, rank, eps, a_pack, a_q8, body, top, idx16, val, ld, ptr, pld, rec, cnt, x_rot, stream
-    "tq_split_prologue_rmsnorm": [_P, _P, _F, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P],
-    "tq_split_gemm_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
-    "tq_split_gemm_mma_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P],
+    "tq_split_prologue": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P],
+    # x, gamma, rms_eps, M, K, had, R, rank, eps, a_pack, a_q8, body, top, idx16, val, ld, ptr, pld, rec, cnt, dense, x_rot, stream
+    "tq_split_prologue_rmsnorm": [_P, _P, _F, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P],
+    "tq_split_gemm_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "tq_split_gemm_mma_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "tq_topr_pack": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P],
     "tq_prepare_weight": [_P, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P],
     "tq_int4_matmul": [_P, _P, _P, _I, _I, _I, _I, _P],

@@ -19,7 +19,7 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
                  uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale, uint16_t* tail_idx16,
                  void* tail_val, int tail_ld, uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt,
                  int32_t* idx32, int8_t* top_q, void* x_rot, const void* gamma, float rms_eps, cudaStream_t st,
-                 int dtype = TQ_BF16);
+                 int dtype = TQ_BF16, void* tail_dense = nullptr);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

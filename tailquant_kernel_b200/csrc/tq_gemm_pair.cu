@@ -34,6 +34,7 @@ constexpr int P_LOOK = 2;  // K slices of the next tile prepared before a tile's
 struct PairGemmParams {
   int M, N, K, R, ld, ptr_ld;
   int tiles_m, tiles_n, kb_total, has_tail;
+  int dense;             // the zero-filled tail matrix is available (tmap_d): half slices with long runs load it
   const uint16_t* idx;   // [M, ld] ascending tail indices (only read for runs longer than the record capacity)
   const uint16_t* val;   // [M, ld] tail values
   const uint16_t* ptr;   // [M, ptr_ld] ptr[m][j] = entries of row m with index < 128 j
@@ -71,7 +72,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 template <int ACT>  // 0: out [M, N]; 1: SwiGLU over interleaved (gate, up) channel pairs, out [M, N/2]
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_constant__ CUtensorMap tmap_b4,
-                  const __grid_constant__ CUtensorMap tmap_w, const PairGemmParams p) {
+                  const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_d,
+                  const PairGemmParams p) {
   using S = PS;
   constexpr int BN = P_BN;
   extern __shared__ unsigned char smem_dyn[];
@@ -106,6 +108,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a8)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b4)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_d)) : "memory");
     for (int s = 0; s < S::SP; ++s) {
       mbar_init(full_p(s), 1);
       mbar_init(empty_p(s), 4);
@@ -437,12 +440,25 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
         if (!TQ_WAIT(9, mbar_wait(empty_u(s), par_of(q) ^ 1u, abort_flag, 0x200000u))) return false;
         if (brow == 0) TQ_TRACE(4, q, 1);
         tc_fence_after();
+        const int nwmax = __reduce_max_sync(0xffffffffu, n);
+        if (p.dense && nwmax > C) {
+          // a run longer than the record among the warp's 32 rows and the zero-filled tail matrix at hand: its 32 x 64
+          // block is the operand itself -- one tiled load (same 128-byte swizzle as the tile), whose bytes the slot's
+          // barrier counts on top of this warp's arrival
+          if (lane == 0) {
+            const int i = g / kbt, kb = g - i * kbt;
+            mbar_arrive_expect_tx_cluster(lead(full_u(s)), 32u * 128u);
+            tma_load_2d_pair(base + s * S::SLOT + (uint32_t)(brow >> 5) * 4096u, &tmap_d, kb * P_BK + 64 * half,
+                             (2 * tile_mt(i) + (int)rank) * P_BM + (brow & ~31), lead(full_u(s)));
+          }
+          return true;
+        }
         unsigned char* arow = sm + s * S::SLOT + roff;
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(arow + ((c ^ (brow & 7)) << 4)) = z;
         if (brow == 0) TQ_TRACE(5, q, 2);
-        const int nmax = __reduce_max_sync(0xffffffffu, min(n, C));  // warp-uniform trip count
+        const int nmax = min(nwmax, C);  // warp-uniform trip count
 #pragma unroll
         for (int j = 0; j < C; ++j) {
           if (j < nmax) {
@@ -530,7 +546,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a8, const __grid_const
 }
 
 template <int ACT>
-int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot, PairGemmParams p, cudaStream_t st) {
+int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot, const void* tail_dense, PairGemmParams p,
+                     cudaStream_t st) {
   using S = PS;
   static bool configured[64] = {};
   int dev = 0;
@@ -543,7 +560,7 @@ int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot
     }
     if (dev < 64) configured[dev] = true;
   }
-  CUtensorMap ma, mb, mw;
+  CUtensorMap ma, mb, mw, md;
   if (!make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_q8, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)p.K, 128,
                           P_BM, true))
     return TQ_ERR_CUDA;
@@ -554,6 +571,15 @@ int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot
   if (!make_tensor_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, wsrc, (uint64_t)(p.has_tail ? p.K : p.K / 4),
                           (uint64_t)p.N, (uint64_t)(p.has_tail ? p.K * 2 : p.K / 2), 64, P_BH, true))
     return TQ_ERR_CUDA;
+  // the zero-filled tail matrix, 32 rows x one 64-wide half slice per load (rows beyond M read as zeros)
+  p.dense = (p.has_tail && tail_dense) ? 1 : 0;
+  if (p.dense) {
+    if (!make_tensor_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, tail_dense, (uint64_t)p.K, (uint64_t)p.M,
+                            (uint64_t)p.K * 2, 64, 32, true))
+      return TQ_ERR_CUDA;
+  } else {
+    md = mw;  // never used; kept valid
+  }
   p.tiles_m = (p.M + 2 * P_BM - 1) / (2 * P_BM);
   p.tiles_n = (p.N + P_BN - 1) / P_BN;
   p.kb_total = p.K / P_BK;
@@ -561,7 +587,7 @@ int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int total = p.tiles_m * p.tiles_n;
   const int pairs = total < sms / 2 ? total : sms / 2;
-  pair_gemm_kernel<ACT><<<2 * pairs, P_THREADS, S::DYN, st>>>(ma, mb, mw, p);
+  pair_gemm_kernel<ACT><<<2 * pairs, P_THREADS, S::DYN, st>>>(ma, mb, mw, md, p);
   return check_launch();
 }
 
@@ -570,9 +596,9 @@ int launch_pair_gemm(const int8_t* a_q8, const uint8_t* b_col, const void* w_rot
 // Runs the pair kernel when the problem has enough 256 x 256 tiles to fill the machine; `*used` says whether it did.
 int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
                   const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
-                  const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
-                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, int act,
-                  cudaStream_t st) {
+                  const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt,
+                  const void* tail_dense, int R, const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail,
+                  int M, int N, int K, int act, cudaStream_t st) {
   PairGemmParams p = {};
   p.M = M;
   p.N = N;
@@ -592,7 +618,9 @@ int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_
   p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
   p.dbg_acc = dbg_acc;
   p.dbg_tail = dbg_tail;
-  return act ? launch_pair_gemm<1>(a_q8, b_col, w_rot, p, st) : launch_pair_gemm<0>(a_q8, b_col, w_rot, p, st);
+  if (tail_dense && !aligned16(tail_dense)) return TQ_ERR_MISALIGNED;
+  return act ? launch_pair_gemm<1>(a_q8, b_col, w_rot, tail_dense, p, st)
+             : launch_pair_gemm<0>(a_q8, b_col, w_rot, tail_dense, p, st);
 }
 
 }  // namespace tq

@@ -529,9 +529,9 @@ namespace tq {
 static int g_gemm_pair_mode = -1;
 int run_pair_gemm(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col, const float* w_scale,
                   const void* w_rot, const uint16_t* tail_idx16, const void* tail_val, int tail_ld,
-                  const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt, int R,
-                  const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, int act,
-                  cudaStream_t st);
+                  const uint16_t* tail_ptr, int ptr_ld, const uint32_t* tail_rec, const uint16_t* tail_cnt,
+                  const void* tail_dense, int R, const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail,
+                  int M, int N, int K, int act, cudaStream_t st);
 }
 
 #ifdef TQ_GEMM_PROFILE
@@ -568,9 +568,9 @@ namespace tq {
 static int run_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                               const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
                               const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
-                              const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
-                              void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, int act,
-                              void* stream) {
+                              const uint32_t* tail_rec, const uint16_t* tail_cnt, const void* tail_dense, int R,
+                              const float* bias, void* out_bf16, int32_t* dbg_acc, float* dbg_tail, int M, int N, int K,
+                              int act, void* stream) {
   if (!a_q8 || !body_scale || !b_col || !w_scale || !out_bf16 || M < 0 || N <= 0 || K <= 0 || R < 0 || R >= K)
     return TQ_ERR_BAD_ARG;
   if (R > 0 && (!w_rot || !tail_idx16 || !tail_val || tail_ld < R || !tail_ptr || ptr_ld < K / G_BK + 1 || !tail_rec ||
@@ -592,8 +592,10 @@ static int run_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const
     const bool pair = g_gemm_pair_mode == 1 || (g_gemm_pair_mode < 0 && (R == 0 || tiles_single > 74));
     if (pair)
       return run_pair_gemm(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld,
-                           tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, act, (cudaStream_t)stream);
+                           tail_rec, tail_cnt, tail_dense, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, act,
+                           (cudaStream_t)stream);
   }
+  // (the one-CTA kernel serves small problems and always walks the row's list for runs longer than a record)
   SplitGemmParams p = {};
   p.act = act;
   p.M = M;
@@ -625,18 +627,20 @@ static int run_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const
 extern "C" int tq_split_gemm_mma(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                                  const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
                                  const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
-                                 const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
-                                 void* out_bf16,
+                                 const uint32_t* tail_rec, const uint16_t* tail_cnt, const void* tail_dense, int R,
+                                 const float* bias, void* out_bf16,
                                  int32_t* dbg_acc, float* dbg_tail, int M, int N, int K, void* stream) {
   return tq::run_split_gemm_mma(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr,
-                                ptr_ld, tail_rec, tail_cnt, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, 0, stream);
+                                ptr_ld, tail_rec, tail_cnt, tail_dense, R, bias, out_bf16, dbg_acc, dbg_tail, M, N, K, 0,
+                                stream);
 }
 
 extern "C" int tq_split_gemm_mma_swiglu(const int8_t* a_q8, const float* body_scale, const uint8_t* b_col,
                                         const float* w_scale, const void* w_rot, const uint16_t* tail_idx16,
                                         const void* tail_val, int tail_ld, const uint16_t* tail_ptr, int ptr_ld,
-                                        const uint32_t* tail_rec, const uint16_t* tail_cnt, int R, const float* bias,
-                                        void* out_bf16, int M, int N, int K, void* stream) {
+                                        const uint32_t* tail_rec, const uint16_t* tail_cnt, const void* tail_dense,
+                                        int R, const float* bias, void* out_bf16, int M, int N, int K, void* stream) {
   return tq::run_split_gemm_mma(a_q8, body_scale, b_col, w_scale, w_rot, tail_idx16, tail_val, tail_ld, tail_ptr,
-                                ptr_ld, tail_rec, tail_cnt, R, bias, out_bf16, nullptr, nullptr, M, N, K, 1, stream);
+                                ptr_ld, tail_rec, tail_cnt, tail_dense, R, bias, out_bf16, nullptr, nullptr, M, N, K, 1,
+                                stream);
 }

@@ -452,6 +452,21 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
           }
         }
       }
+      if (p.tail_dense) {
+        // the row with everything outside the tail zeroed (operand rows for the fused GEMM's dense half slices)
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          const int g = tid + NT * j;
+          if ((GN % NT == 0) || g < GN) {
+            uint32_t o[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              o[c] = (((tm[j] >> (2 * c)) & 1u) ? (pk[8 * j + 2 * c] >> 16) : 0u) |
+                     (((tm[j] >> (2 * c + 1)) & 1u) ? (pk[8 * j + 2 * c + 1] & 0xffff0000u) : 0u);
+            *reinterpret_cast<uint4*>(p.tail_dense + (size_t)m * K + 8 * g) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
       __syncthreads();
       // entries of the row's ascending list before a half slice: the larger keys, plus the ties that made it
       auto half_start = [&](int hs) -> int {
@@ -617,14 +632,15 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
                  uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale, uint16_t* tail_idx16,
                  void* tail_val, int tail_ld, uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt,
                  int32_t* idx32, int8_t* top_q, void* x_rot, const void* gamma, float rms_eps, cudaStream_t st,
-                 int dtype) {
+                 int dtype, void* tail_dense) {
   if ((tail_idx16 || tail_val) && tail_ld < R) return TQ_ERR_BAD_ARG;
   if (gamma && !aligned16(gamma)) return TQ_ERR_MISALIGNED;
   if (tail_ptr && (ptr_ld < K / 128 + 1 || K % 128 != 0)) return TQ_ERR_BAD_ARG;
   if ((tail_rec != nullptr) != (tail_cnt != nullptr) || (tail_rec && K % 128 != 0)) return TQ_ERR_BAD_ARG;
   if (!x || (!a_pack && !a_q8) || !body_scale || M < 0 || K <= 0 || R < 0 || R >= K) return TQ_ERR_BAD_ARG;
   if (dr < 1 || dr > K) return TQ_ERR_BAD_ARG;
-  if (!aligned16(x) || (a_pack && !aligned16(a_pack)) || (a_q8 && !aligned16(a_q8)) || (x_rot && !aligned16(x_rot)))
+  if (!aligned16(x) || (a_pack && !aligned16(a_pack)) || (a_q8 && !aligned16(a_q8)) || (x_rot && !aligned16(x_rot)) ||
+      (tail_dense && !aligned16(tail_dense)))
     return TQ_ERR_MISALIGNED;
   if (M == 0) return TQ_OK;
   PrologueParams p;
@@ -649,6 +665,7 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
   p.idx32 = idx32;
   p.top_q = top_q;
   p.x_rot = reinterpret_cast<uint16_t*>(x_rot);
+  p.tail_dense = reinterpret_cast<uint16_t*>(tail_dense);
   p.gamma = reinterpret_cast<const uint16_t*>(gamma);
   p.rms_eps = rms_eps;
   // the kernel specialised for the benchmarked widths first (same outputs bit for bit); everything else, and
@@ -676,11 +693,11 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
 extern "C" int tq_split_prologue(const void* x, int M, int K, int had_kind, int R, int descending_rank,
                                  float eps, uint8_t* a_pack, int8_t* a_q8, float* body_scale, float* top_scale,
                                  uint16_t* tail_idx16, void* tail_val, int tail_ld, uint16_t* tail_ptr,
-                                 int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt, int32_t* idx32, int8_t* top_q,
-                                 void* x_rot, void* stream) {
+                                 int ptr_ld, uint32_t* tail_rec, uint16_t* tail_cnt, void* tail_dense, int32_t* idx32,
+                                 int8_t* top_q, void* x_rot, void* stream) {
   return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, a_q8, body_scale, top_scale,
                           tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld, tail_rec, tail_cnt, idx32, top_q, x_rot,
-                          nullptr, 0.0f, (cudaStream_t)stream, TQ_BF16);
+                          nullptr, 0.0f, (cudaStream_t)stream, TQ_BF16, tail_dense);
 }
 
 extern "C" int tq_set_prologue_mode(int mode) {
@@ -693,11 +710,11 @@ extern "C" int tq_split_prologue_rmsnorm(const void* x, const void* gamma, float
                                          int R, int descending_rank, float eps, uint8_t* a_pack, int8_t* a_q8,
                                          float* body_scale, float* top_scale, uint16_t* tail_idx16, void* tail_val,
                                          int tail_ld, uint16_t* tail_ptr, int ptr_ld, uint32_t* tail_rec,
-                                         uint16_t* tail_cnt, void* x_rot, void* stream) {
+                                         uint16_t* tail_cnt, void* tail_dense, void* x_rot, void* stream) {
   if (!gamma) return TQ_ERR_BAD_ARG;
   return tq::run_prologue(x, M, K, had_kind, R, descending_rank, eps, 0, a_pack, a_q8, body_scale, top_scale,
                           tail_idx16, tail_val, tail_ld, tail_ptr, ptr_ld, tail_rec, tail_cnt, nullptr, nullptr, x_rot,
-                          gamma, rms_eps, (cudaStream_t)stream, TQ_BF16);
+                          gamma, rms_eps, (cudaStream_t)stream, TQ_BF16, tail_dense);
 }
 
 extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int descending_rank,
@@ -707,5 +724,5 @@ extern "C" int tq_topr_pack(const void* A, int dtype, int M, int K, int R, int d
   if (R > 0 && (!top_q || !idx || !top_scale)) return TQ_ERR_BAD_ARG;
   return tq::run_prologue(A, M, K, TQ_HAD_NONE, R, descending_rank, eps, 0, A_pack, nullptr, body_scale, top_scale,
                           nullptr, nullptr, 0, nullptr, 0, nullptr, nullptr, idx, top_q, nullptr, nullptr, 0.0f,
-                          (cudaStream_t)stream, dtype);
+                          (cudaStream_t)stream, dtype, nullptr);
 }

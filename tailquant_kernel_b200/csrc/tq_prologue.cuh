@@ -27,6 +27,7 @@ struct PrologueParams {
   int32_t* idx32;
   int8_t* top_q;
   uint16_t* x_rot;
+  uint16_t* tail_dense;   // [M, K] bf16: the rotated row with every element outside the tail set to zero (R > 0), or NULL
   const uint16_t* gamma;  // [K] bf16 RMSNorm weight, or NULL: x is used as it is
   float rms_eps;
 };

@@ -676,6 +676,21 @@ prologue_fast_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrologueP
         }
       }
       const int ntail = __popc(tm[0]) + __popc(tm[1]);
+      if (p.tail_dense) {
+        // the row with everything outside the tail zeroed: the operand rows that the fused GEMM loads by TMA where a
+        // half slice holds more entries than a record
+        uint4* dst = reinterpret_cast<uint4*>(p.tail_dense + (size_t)m * K + 64 * tid);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int j = 4 * c + i;
+            o[i] = w[j] & (((tm[j >> 4] >> (j & 15)) & 0x00010001u) * 0xffffu);
+          }
+          dst[c] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
       if (p.tail_ptr) {  // run boundaries of the row's ascending index list at multiples of 128
         if ((tid & 1) == 0) p.tail_ptr[(size_t)m * p.ptr_ld + (tid >> 1)] = (uint16_t)tail_before;
         if (tid == 0) p.tail_ptr[(size_t)m * p.ptr_ld + NSL] = (uint16_t)R;

@@ -44,7 +44,7 @@ class _Workspace:
     another layer's prologue) and the layer's own output and scratch."""
 
     def __init__(self, M: int, K: int, N: int, R: int, device, mma: bool, small: bool, n_out: Optional[int] = None,
-                 with_pro: bool = True):
+                 with_pro: bool = True, dense: bool = False):
         ld = (R + 7) // 8 * 8
         q8 = mma and not small  # the fused GEMM takes INT8 codes; the decode GEMV is faster on the packed form
         self.M, self.K, self.R, self.q8 = M, K, R, q8
@@ -60,6 +60,9 @@ class _Workspace:
             top_scale=torch.empty(M, dtype=torch.float32, device=device),
             tail_idx=torch.zeros((M, ld), dtype=torch.int16, device=device) if R else None,
             tail_val=torch.zeros((M, ld), dtype=torch.bfloat16, device=device) if R else None,
+            # block-diagonal rotations leave the tail concentrated in a few 128-blocks: the fused GEMM then loads
+            # whole operand rows of the zero-filled tail matrix instead of walking long runs entry by entry
+            tail_dense=torch.empty((M, K), dtype=torch.bfloat16, device=device) if (dense and q8 and R) else None,
             R=R)
         self.tail = torch.empty((M, N), dtype=torch.float32, device=device) if (R and not mma) else None
         self.acc = None  # int32 [splits, M, N], decode path only
@@ -179,7 +182,8 @@ class SplitLinear:
         ws = self._ws.get(M)
         if ws is None:
             ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M),
-                                          M <= self.small_m, self.N_out)
+                                          M <= self.small_m, self.N_out,
+                                          dense=self.w.had_kind == ops.TQ_HAD_BLOCK128)
         return ws
 
     def _own_buffers(self, ws: _Workspace, M: int) -> _Workspace:

@@ -106,12 +106,14 @@ class PrologueOut:
     tail_ptr: Optional[torch.Tensor] = None  # [M, K/128 + 1] int16 storage of u16 run boundaries
     tail_rec: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 128, TAIL_REC_CAP] int32: tile position | bf16 << 16
     tail_cnt: Optional[torch.Tensor] = None  # [2 ceil(M/256), K/64, 128] int16: entries per (row, 64-wide half slice)
+    tail_dense: Optional[torch.Tensor] = None  # [M, K] bf16: the rotated row, zero outside the tail (R > 0)
 
 
 def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Optional[int] = None,
                    eps: float = EPS, t16: bool = True, t4: bool = False, want_x_rot: bool = False,
                    want_q8: bool = False, want_pack: bool = True, out: Optional[PrologueOut] = None,
-                   rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6) -> PrologueOut:
+                   rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
+                   want_dense: bool = False) -> PrologueOut:
     """Rotation + per-token INT4 + top-R tail split of x [M,K] bf16 in one kernel.  With `rms_weight` ([K] bf16)
     an RMSNorm is applied to x first, inside the same kernel (no T4 outputs then)."""
     _check_cuda(x, "x", torch.bfloat16)
@@ -138,6 +140,7 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
             idx32=torch.empty((M, R), dtype=torch.int32, device=dev) if (t4 and R) else None,
             top_q=torch.empty((M, R), dtype=torch.int8, device=dev) if (t4 and R) else None,
             x_rot=torch.empty((M, K), dtype=torch.bfloat16, device=dev) if want_x_rot else None,
+            tail_dense=torch.empty((M, K), dtype=torch.bfloat16, device=dev) if (want_dense and R) else None,
         )
     ld = out.tail_idx.shape[1] if out.tail_idx is not None else 0
     pld = out.tail_ptr.shape[1] if out.tail_ptr is not None else 0
@@ -148,13 +151,14 @@ def split_prologue(x: torch.Tensor, had_kind: int, R: int, descending_rank: Opti
         rc = _lib.load().tq_split_prologue_rmsnorm(
             _ptr(x), _ptr(rms_weight), float(rms_eps), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack),
             _ptr(out.a_q8), _ptr(out.body_scale), _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld,
-            _ptr(out.tail_ptr), pld, _ptr(out.tail_rec), _ptr(out.tail_cnt), _ptr(out.x_rot), _stream())
+            _ptr(out.tail_ptr), pld, _ptr(out.tail_rec), _ptr(out.tail_cnt), _ptr(out.tail_dense), _ptr(out.x_rot),
+            _stream())
         _lib.check(rc, f"split_prologue_rmsnorm(M={M}, K={K}, had_kind={had_kind}, R={R})")
         return out
     rc = _lib.load().tq_split_prologue(
         _ptr(x), M, K, had_kind, R, descending_rank, eps, _ptr(out.a_pack), _ptr(out.a_q8), _ptr(out.body_scale),
         _ptr(out.top_scale), _ptr(out.tail_idx), _ptr(out.tail_val), ld, _ptr(out.tail_ptr), pld, _ptr(out.tail_rec),
-        _ptr(out.tail_cnt), _ptr(out.idx32), _ptr(out.top_q), _ptr(out.x_rot), _stream())
+        _ptr(out.tail_cnt), _ptr(out.tail_dense), _ptr(out.idx32), _ptr(out.top_q), _ptr(out.x_rot), _stream())
     _lib.check(rc, f"split_prologue(M={M}, K={K}, had_kind={had_kind}, R={R})")
     return out
 
@@ -311,13 +315,16 @@ def split_gemm_mma(a_q8, body_scale, B_pack, w_scale, out, w_rot=None, pro: Opti
         _check(tuple(tail_rec.shape) == (2 * ((M + 255) // 256), K // 64, 128, TAIL_REC_CAP), "tail_rec has the wrong shape")
         _check(tuple(tail_cnt.shape) == (2 * ((M + 255) // 256), K // 64, 128), "tail_cnt has the wrong shape")
         ld = tail_idx.shape[1]
+        if pro.tail_dense is not None:
+            _check_cuda(pro.tail_dense, "tail_dense", torch.bfloat16)
+            _check(tuple(pro.tail_dense.shape) == (M, K), "tail_dense must be [M, K]")
     if bias is not None:
         _check_cuda(bias, "bias", torch.float32)
     common = (_ptr(a_q8), _ptr(body_scale), _ptr(B_pack), _ptr(w_scale),
               _ptr(w_rot) if R else None, _ptr(tail_idx) if R else None,
               _ptr(tail_val) if R else None, ld, _ptr(tail_ptr) if R else None,
               tail_ptr.shape[1] if R else 0, _ptr(tail_rec) if R else None,
-              _ptr(tail_cnt) if R else None, int(R), _ptr(bias), _ptr(out))
+              _ptr(tail_cnt) if R else None, _ptr(pro.tail_dense) if R else None, int(R), _ptr(bias), _ptr(out))
     if act == "swiglu":
         rc = _lib.load().tq_split_gemm_mma_swiglu(*common, M, N, K, _stream())
     else:

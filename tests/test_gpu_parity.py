@@ -102,7 +102,7 @@ def test_prologue_parity(kind, K, M, R, data, pct):
     xb = make_x(M, K, seed=K + M + R, kind=data)
     _, dr, _ = O.split_select_params(K, R, pct)
     ref = O.prologue(xb, kind, R, dr)
-    out = ops.split_prologue(dev_bf16(xb), kind, R, dr, t16=True, t4=True, want_x_rot=True)
+    out = ops.split_prologue(dev_bf16(xb), kind, R, dr, t16=True, t4=True, want_x_rot=True, want_dense=True)
     torch.cuda.synchronize()
     assert np.array_equal(host_bits(out.x_rot), ref.x_rot), "rotated bf16 values"
     assert np.array_equal(out.body_scale.cpu().numpy(), ref.body_scale), "body scale"
@@ -112,6 +112,9 @@ def test_prologue_parity(kind, K, M, R, data, pct):
         assert np.array_equal(host_bits(out.tail_val)[:, :R], ref.tail_val), "tail values"
         assert np.array_equal(out.idx32.cpu().numpy(), ref.idx), "int32 indices"
         assert np.array_equal(out.top_q.cpu().numpy(), ref.top_q), "tail INT4 codes"
+        dense = np.zeros((M, K), np.uint16)
+        np.put_along_axis(dense, ref.idx.astype(np.int64), ref.tail_val, axis=1)
+        assert np.array_equal(host_bits(out.tail_dense), dense), "zero-filled tail matrix"
     assert np.array_equal(out.a_pack.cpu().numpy(), ref.a_pack), "packed INT4 codes"
 
 
@@ -135,7 +138,7 @@ def test_specialised_prologue_equals_general_kernel(kind, K, R, pct, data):
     for mode in (0, -1):
         ops.set_prologue_mode(mode)
         try:
-            a = ops.split_prologue(x, kind, R, dr, t16=True, t4=True, want_x_rot=True, want_q8=True)
+            a = ops.split_prologue(x, kind, R, dr, t16=True, t4=True, want_x_rot=True, want_q8=True, want_dense=True)
             torch.cuda.synchronize()
         finally:
             ops.set_prologue_mode(-1)
@@ -143,7 +146,7 @@ def test_specialised_prologue_equals_general_kernel(kind, K, R, pct, data):
     g, f = outs
     names = ["x_rot", "a_pack", "a_q8", "body_scale", "top_scale"]
     if R:
-        names += ["tail_idx", "tail_val", "idx32", "top_q", "tail_ptr", "tail_cnt"]
+        names += ["tail_idx", "tail_val", "idx32", "top_q", "tail_ptr", "tail_cnt", "tail_dense"]
     for n in names:
         assert torch.equal(getattr(g, n).view(torch.uint8), getattr(f, n).view(torch.uint8)), n
     if R:
@@ -423,6 +426,19 @@ def test_prologue_int8_operand(kind, K, M, R):
 def test_split_gemm_mma(M, N, K, R, bias, cluster, pair):
     """Fused kernel: int32 accumulators bit-exact, tensor-core tail within fp32 accumulation error of the
     fixed-order chain, bf16 output within the stated bounds."""
+    _run_split_gemm_mma(M, N, K, R, bias, cluster, pair, dense=False)
+
+
+@pytest.mark.parametrize("M,N,K,R,cluster", [(140, 264, 1024, 205, True), (300, 520, 1024, 205, "mixed"),
+                                             (2304, 512, 384, 60, "mixed"), (300, 1032, 4096, 205, False)])
+def test_split_gemm_mma_with_the_zero_filled_tail_matrix(M, N, K, R, cluster):
+    """The CTA-pair kernel given the zero-filled tail matrix: 32-row blocks of a half slice in which a row has more
+    entries than a record are loaded from it (all of them in the clustered case, every other block in the mixed one,
+    almost none with uniform positions) -- same results as from the records and lists."""
+    _run_split_gemm_mma(M, N, K, R, False, cluster, 1, dense=True)
+
+
+def _run_split_gemm_mma(M, N, K, R, bias, cluster, pair, dense):
     rng = np.random.default_rng(M + N + K + R)
     qa, qw = rand_codes(rng, M, K), rand_codes(rng, N, K)
     sx = rng.uniform(0.001, 0.02, M).astype(np.float32)
@@ -437,7 +453,9 @@ def test_split_gemm_mma(M, N, K, R, bias, cluster, pair):
     if R:
         idx = np.sort(np.argsort(rng.random((M, K)), axis=1)[:, :R], axis=1).astype(np.int32)
         if cluster:  # runs far longer than a slice record: entries packed into the first slices
-            idx = np.tile(np.arange(R, dtype=np.int32) + 3, (M, 1))
+            packed = np.tile(np.arange(R, dtype=np.int32) + 3, (M, 1))
+            rows = np.ones(M, bool) if cluster is True else (np.arange(M) % 64 < 32) | (np.arange(M) % 97 == 40)
+            idx[rows] = packed[rows]
         val = O.f32_to_bf16_bits(rng.standard_normal((M, R), dtype=np.float32) * 3)
         for r_ in range(M):  # tail positions carry code 0 in the dense operand, as the prologue guarantees
             qa[r_, idx[r_]] = 0
@@ -456,6 +474,10 @@ def test_split_gemm_mma(M, N, K, R, bias, cluster, pair):
         pro = ops.PrologueOut(a_pack=None, body_scale=g(sx), top_scale=g(sx), tail_idx=g(ti.view(np.int16)),
                               tail_val=dev_bf16(tv), R=R, tail_ptr=g(ptr.view(np.int16)), tail_rec=g(rec.view(np.int32)),
                               tail_cnt=g(cnt.view(np.int16)))
+        if dense:
+            td = np.zeros((M, K), np.uint16)
+            np.put_along_axis(td, idx.astype(np.int64), val, axis=1)
+            pro.tail_dense = dev_bf16(td)
     out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     dacc = torch.empty((M, N), dtype=torch.int32, device="cuda")
     dtail = torch.empty((M, N), dtype=torch.float32, device="cuda")
@@ -751,6 +773,15 @@ def test_fused_gemm_at_benchmark_shapes(name, M, K, N, kind, R, n_out):
                        R=R, dbg_acc=dacc, dbg_tail=dtail)
     torch.cuda.synchronize()
     assert torch.equal(y, y2), "the run with the debug outputs must give the same bf16 bits"
+    if kind == O.HAD_BLOCK128:  # long runs per half slice: served from the zero-filled tail matrix, or from the lists
+        import dataclasses
+        assert ws.pro.tail_dense is not None
+        assert int((ws.pro.tail_cnt > ops.TAIL_REC_CAP).sum()) > 0, "this input must have runs longer than a record"
+        y3 = torch.empty_like(y2)
+        ops.split_gemm_mma(ws.pro.a_q8, ws.pro.body_scale, lin.w.b_col, lin.w.w_scale, y3, w_rot=lin.w.w_rot,
+                           pro=dataclasses.replace(ws.pro, tail_dense=None), R=R)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y3), "tail matrix and tail lists must give the same bf16 bits"
     # ---- oracle on the sample
     wq = O.prepare_weight(wb[chan], kind)
     ref = O.prologue(xb[rows], kind, R)

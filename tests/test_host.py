@@ -34,7 +34,7 @@ def test_argument_errors_need_no_gpu():
     import ctypes
     from tailquant_kernel_b200 import _lib
     lib = _lib.load()
-    assert lib.tq_split_prologue(None, 1, 4096, 1, 0, 1, 1e-8, None, None, None, None, None, None, 0, None, 0, None, None, None, None, None, None) == -1
+    assert lib.tq_split_prologue(None, 1, 4096, 1, 0, 1, 1e-8, None, None, None, None, None, None, 0, None, 0, None, None, None, None, None, None, None) == -1
     assert lib.tq_int4_matmul(None, None, None, 1, 8, 128, 1, None) == -1
     buf = ctypes.create_string_buffer(64)
     p = ctypes.addressof(buf) & ~15
