@@ -20,7 +20,7 @@ def test_library_exports_every_declared_symbol():
     build.build()
     lib = _lib.load()
     header = open(os.path.join(ROOT, "include", "tailquant.h")).read()
-    declared = set(re.findall(r"^\s*(?:int|const char\*)\s+(tq_\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^\s*(?:int|long long|const char\*)\s+(tq_\w+)\s*\(", header, flags=re.M))
     assert declared, "no declarations parsed"
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
     for name in declared:
