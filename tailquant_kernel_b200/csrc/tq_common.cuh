@@ -23,30 +23,6 @@ int run_prologue(const void* x, int M, int K, int had_kind, int R, int dr, float
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// ---------------------------------------------------------------------------- programmatic dependent launch
-// A kernel launched with `launch_after_primary` may start while the kernel in front of it in the stream is still
-// running (as soon as that one has executed pdl_launch_dependents() in every CTA, or ended); everything it does
-// before pdl_wait() must be independent of earlier work -- e.g. fetching weights -- and pdl_wait() returns once the
-// earlier kernels have completed and their writes are visible.  Without the launch attribute both calls do nothing.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_after_primary(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                                        Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
-}
-
 // ---------------------------------------------------------------------------- bf16 bits
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits) { return __uint_as_float(bits << 16); }
 

@@ -56,7 +56,6 @@ gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b
   const int g = lane >> 2, j = lane & 3;
   const int k0 = blockIdx.y * k_per_split;
   const int k1 = min(K, k0 + k_per_split);
-  pdl_launch_dependents();  // a following weight-streaming kernel may start fetching its weights under this one
   if (k0 >= k1) return;
   C += (size_t)blockIdx.y * (size_t)pstride;  // partial-sum mode: one [M, N] slab per K range (pstride = M * N)
   static_assert(A8 || !SRC8, "INT8 input is staged as bytes");
@@ -83,12 +82,6 @@ gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b
       wq[s] = (s < nslices && n < N) ? ldg_nc_128(wrow + (size_t)s * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
 
     if (cg == 0) {
-      // Launched ahead of the end of the kernel that writes the activations (the prologue): the first weight loads
-      // are in flight, the rest of the CTA's weight range is requested into L2, and only now the CTA waits for
-      // that kernel.  (Nothing above reads or writes anything an earlier kernel touches.)
-      for (int s = PF + 2 * j; s < nslices; s += 8)
-        if (n < N) asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow - j * 16 + (size_t)s * (DV_KS / 2)));
-      pdl_wait();
       const int in_bytes = (k1 - k0) / SB;  // input bytes per row in this range
       for (int i = tid; i < 16 * MT * (in_bytes / 16); i += DV_THREADS) {
         const int row = i / (in_bytes / 16), piece = i % (in_bytes / 16);
@@ -258,13 +251,8 @@ int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, 
       return TQ_ERR_CUDA;
     }
   }
-  const cudaError_t e = launch_after_primary(kern, grid, dim3(DV_THREADS), smem, st, a_pack, b_col, C, M, N, K, kps,
-                                             (splits == 1 || partials) ? 1 : 0, cgroups,
+  kern<<<grid, DV_THREADS, smem, st>>>(a_pack, b_col, C, M, N, K, kps, (splits == 1 || partials) ? 1 : 0, cgroups,
                                              partials ? (long long)M * N : 0ll);
-  if (e != cudaSuccess) {
-    set_last_cuda_error(e);
-    return TQ_ERR_CUDA;
-  }
   return check_launch();
 }
 

@@ -226,7 +226,6 @@ __global__ void __launch_bounds__(NT, min_ctas(K)) prologue_kernel(const Prologu
   uint16_t* st_val = st_idx + Rpad;
   int8_t* st_q = reinterpret_cast<int8_t*>(st_val + Rpad);
 
-  pdl_launch_dependents();  // (a weight-streaming kernel behind this one may start fetching its weights)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int R = p.R;
   const int fbase = BLOCK ? ((tid & 15) + 128 * (tid >> 4)) : tid;  // index = fbase + eoff(e)

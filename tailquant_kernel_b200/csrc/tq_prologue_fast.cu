@@ -287,7 +287,6 @@ prologue_fast_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrologueP
   const uint32_t bar = base + S::BAR_OFF;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + S::BAR_OFF + 8);
 
-  pdl_launch_dependents();  // (a weight-streaming kernel behind this one may start fetching its weights)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int R = p.R;
   const smp my_row = rowbuf + tid * 128;
