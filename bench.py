@@ -643,7 +643,7 @@ def run_extra(args) -> None:
                 t_all = graph_ms_of(lambda: lin.forward(x))
                 # the weight stream is timed with the packed weights rotating through > 300 MB of copies inside
                 # one graph, so that every launch reads them from HBM and not from the 126 MB L2
-                tc = M >= 32 and N >= 6144  # the layer's dispatch: tcgen05 split-K GEMM from 32 rows on the wide projections
+                tc = lin._decode_uses_tc(M)  # the layer's dispatch of the dense part
                 part = torch.empty((_ops.gemv_plan(M, N, K), M, N), dtype=torch.int32, device=dev)
 
                 def all_copies():

@@ -235,6 +235,10 @@ int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t
  * tq_dequant_finish_partials adds the slabs (exactly) and finishes like tq_dequant_finish; act = 1 applies the
  * SwiGLU of tq_split_gemm_mma_swiglu (out [M, N/2]). */
 int tq_int4_gemv_plan(int M, int N, int K, int a_is_int8);
+/* 8-channel tiles that a warp of the GEMV multiplies with one activation fragment: -1 (default) = 1 up to 16 rows, 4
+ * beyond (packed activations), or 1 / 2 / 4 for every call with more than 16 rows.  tq_int4_gemv_plan follows it.
+ * A comparison switch without a reference counterpart. */
+int tq_set_gemv_channel_tiles(int tiles);
 int tq_int4_gemv_partials(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* partials,
                           int M, int N, int K, int splits, void* stream);
 int tq_dequant_finish_partials(const int32_t* partials, int splits, const float* body_scale, const float* w_scale,

@@ -24,6 +24,7 @@ SIGNATURES = {
     "tq_split_prologue": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P],
     # x, gamma, rms_eps, M, K, had, R, rank, eps, a_pack, a_q8, body, top, idx16, val, ld, ptr, pld, rec, cnt, dense, x_rot, stream
     "tq_split_prologue_rmsnorm": [_P, _P, _F, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P],
+    "tq_set_gemv_channel_tiles": [_I],
     "tq_split_gemm_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
     "tq_split_gemm_mma_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "tq_topr_pack": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P],

@@ -47,7 +47,11 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 // bytes in the order widen16 produces, so their fragments are plain loads.  SRC8: they also arrive that way, as
 // true INT8 codes -- the prologue's a_q8 output; otherwise they arrive packed and are widened (value x 16) either
 // while staging (A8; measured slower than per-fragment widening, kept as an instantiation option) or per fragment.
-template <int MT, bool A8, bool SRC8>
+// NB = 8-channel tiles per warp (a CTA owns 64 NB channels).  With more than one 16-row tile of activations the
+// fragment loads from shared memory, not the weight stream, are what a warp spends its time on (64 rows x 128 bytes
+// per K slice against 512 bytes of weights for 8 channels): NB = 4 uses every activation fragment for four channel
+// tiles, a lane then streams the weights of four channels.
+template <int MT, bool A8, bool SRC8, int NB>
 __global__ void __launch_bounds__(DV_THREADS)
 gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b_col, int32_t* __restrict__ C, int M,
                int N, int K, int k_per_split, int direct, int cgroups, long long pstride) {
@@ -66,20 +70,29 @@ gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b
   const int pitch = kbytes + (A8 ? 16 : 64);
 
   const int nslices = (k1 - k0) / DV_KS;
-  constexpr int PF = MT <= 2 ? 8 : 4;  // weight loads kept in flight per lane
+  constexpr int PF = (MT <= 2 ? 8 : 4) / NB > 2 ? (MT <= 2 ? 8 : 4) / NB : 2;  // K slices of weight loads in flight per lane
+  constexpr int CH = DV_CH * NB;       // channels per CTA
   const bool hi_rows = M > 8;  // rows 8..15 of the (only) tile exist
 
   // A CTA goes through `cgroups` groups of 64 channels with the same staged activations.
   for (int cg = 0; cg < cgroups; ++cg) {
-    const int nbase = (blockIdx.x * cgroups + cg) * DV_CH;
+    const int nbase = (blockIdx.x * cgroups + cg) * CH;
     if (nbase >= N) break;
     // the weight stream starts first: it does not depend on the activations
-    const int n = nbase + warp * 8 + g;  // channel whose weights this lane streams
-    const uint8_t* wrow = b_col + (size_t)min(n, N - 1) * (K / 2) + k0 / 2 + j * 16;
-    uint4 wq[PF];
+    const uint8_t* wrow[NB];  // rows of the channels whose weights this lane streams: tile b, row g of the tile
+    bool wok[NB];
+    uint4 wq[PF][NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      const int n = nbase + (warp * NB + b) * 8 + g;
+      wok[b] = n < N;
+      wrow[b] = b_col + (size_t)min(n, N - 1) * (K / 2) + k0 / 2 + j * 16;
+    }
 #pragma unroll
     for (int s = 0; s < PF; ++s)
-      wq[s] = (s < nslices && n < N) ? ldg_nc_128(wrow + (size_t)s * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+        wq[s][b] = (s < nslices && wok[b]) ? ldg_nc_128(wrow[b] + (size_t)s * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
 
     if (cg == 0) {
       const int in_bytes = (k1 - k0) / SB;  // input bytes per row in this range
@@ -99,20 +112,25 @@ gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b
       __syncthreads();
     }
 
-    int acc[MT][4];
+    int acc[MT][NB][4];
 #pragma unroll
     for (int t = 0; t < MT; ++t)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+      for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[t][b][i] = 0;
     for (int s0 = 0; s0 < nslices; s0 += PF) {
 #pragma unroll
       for (int u = 0; u < PF; ++u) {
         const int s = s0 + u;
         if (s < nslices) {
-          uint32_t b[8];
-          widen16(wq[u], b);
+          uint32_t bw[NB][8];
           const int sn = s + PF;
-          wq[u] = (sn < nslices && n < N) ? ldg_nc_128(wrow + (size_t)sn * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            widen16(wq[u][b], bw[b]);
+            wq[u][b] = (sn < nslices && wok[b]) ? ldg_nc_128(wrow[b] + (size_t)sn * (DV_KS / 2)) : make_uint4(0u, 0u, 0u, 0u);
+          }
 #pragma unroll
           for (int t = 0; t < MT; ++t) {
             uint32_t a[8], c[8];
@@ -140,25 +158,31 @@ gemv_s4_kernel(const uint8_t* __restrict__ a_pack, const uint8_t* __restrict__ b
               }
             }
 #pragma unroll
-            for (int qd = 0; qd < 4; ++qd) mma_s8(acc[t], a[2 * qd], c[2 * qd], a[2 * qd + 1], c[2 * qd + 1], b[2 * qd], b[2 * qd + 1]);
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+              for (int qd = 0; qd < 4; ++qd)
+                mma_s8(acc[t][b], a[2 * qd], c[2 * qd], a[2 * qd + 1], c[2 * qd + 1], bw[b][2 * qd], bw[b][2 * qd + 1]);
           }
         }
       }
     }
 
-    // accumulator fragment: rows g and g + 8 of the tile, channels 2j and 2j + 1 of the warp's eight
-    const int nc = nbase + warp * 8 + 2 * j;
+    // accumulator fragment: rows g and g + 8 of the tile, channels 2j and 2j + 1 of the eight of channel tile b
 #pragma unroll
     for (int t = 0; t < MT; ++t) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int row = 16 * t + g + ((i >> 1) << 3), col = nc + (i & 1);
-        if (row < M && col < N) {
-          const int v = acc[t][i] >> (SRC8 ? 4 : 8);  // one or both operands carry a factor 16
-          if (direct)
-            C[(size_t)row * N + col] = v;  // the only K range: no accumulation across CTAs
-          else
-            atomicAdd(C + (size_t)row * N + col, v);
+      for (int b = 0; b < NB; ++b) {
+        const int nc = nbase + (warp * NB + b) * 8 + 2 * j;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = 16 * t + g + ((i >> 1) << 3), col = nc + (i & 1);
+          if (row < M && col < N) {
+            const int v = acc[t][b][i] >> (SRC8 ? 4 : 8);  // one or both operands carry a factor 16
+            if (direct)
+              C[(size_t)row * N + col] = v;  // the only K range: no accumulation across CTAs
+            else
+              atomicAdd(C + (size_t)row * N + col, v);
+          }
         }
       }
     }
@@ -227,11 +251,11 @@ tail_small_kernel(const uint16_t* __restrict__ idx, const uint16_t* __restrict__
   }
 }
 
-template <int MT, bool A8, bool SRC8>
+template <int MT, bool A8, bool SRC8, int NB>
 int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, int N, int K, int kps, int splits,
                 int cgroups, bool partials, cudaStream_t st) {
   const size_t smem = (size_t)16 * MT * (A8 ? kps + 16 : kps / 2 + 64);
-  auto kern = gemv_s4_kernel<MT, A8, SRC8>;
+  auto kern = gemv_s4_kernel<MT, A8, SRC8, NB>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -243,7 +267,7 @@ int launch_gemv(const uint8_t* a_pack, const uint8_t* b_col, int32_t* C, int M, 
     }
     if (dev < 64) configured[dev] = true;
   }
-  dim3 grid((N + DV_CH * cgroups - 1) / (DV_CH * cgroups), splits);
+  dim3 grid((N + DV_CH * NB * cgroups - 1) / (DV_CH * NB * cgroups), splits);
   if (splits > 1 && !partials) {  // partial sums of the K ranges meet in C through atomics
     cudaError_t e = cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(int32_t), st);
     if (e != cudaSuccess) {
@@ -263,20 +287,27 @@ namespace tq {
 namespace {
 
 struct GemvPlan {
-  int sps, splits, mt, cgroups;
+  int sps, splits, mt, cgroups, nb;
 };
+
+int g_gemv_tiles = -1;  // tq_set_gemv_channel_tiles: -1 = by row count, 1 / 2 / 4 = 8-channel tiles per warp
 
 // K ranges of a call: `split_k` < 1 lets the library choose
 GemvPlan plan_gemv(int M, int N, int K, int split_k, bool a8) {
   GemvPlan g;
   const int slices = K / DV_KS;
   g.mt = (M + 15) / 16;
+  // More than 16 rows (packed activations): four channel tiles per warp share every activation fragment.  Timed on
+  // the Qwen3-8B layer shapes with the weights coming from HBM: 17..32 rows -- four tiles ahead everywhere (gate_up
+  // 21 against 26 us, down 11 against 16 us); 33..64 rows -- ahead only where K or N is large, one tile otherwise.
+  g.nb = (a8 || g.mt < 2) ? 1 : (g_gemv_tiles > 0 ? g_gemv_tiles : ((g.mt == 2 || K >= 8192 || N >= 16384) ? 4 : 1));
   // groups of 64 channels per CTA (sharing the staged activations): more than one measured slower at every M
   // on the Qwen3-8B layer shapes -- the smaller grid costs more than the repeated staging
   g.cgroups = 1;
   if (split_k < 1) {  // four CTAs per SM, eight for the wide projections (timed on the Qwen3-8B layer shapes)
-    const int ctas_n = (N + DV_CH * g.cgroups - 1) / (DV_CH * g.cgroups);
-    split_k = ((ctas_n >= 256 ? 8 : 4) * 148 + ctas_n - 1) / ctas_n;
+    const int ctas_n = (N + DV_CH * g.nb * g.cgroups - 1) / (DV_CH * g.nb * g.cgroups);
+    const int per_sm = g.nb == 1 ? (ctas_n >= 256 ? 8 : 4) : 2;
+    split_k = (per_sm * 148 + ctas_n - 1) / ctas_n;
   }
   if (split_k > slices) split_k = slices;
   g.sps = (slices + split_k - 1) / split_k;  // slices per split
@@ -299,15 +330,20 @@ int run_gemv(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, in
   if (partials && split_k >= 1 && g.splits != split_k) return TQ_ERR_BAD_ARG;  // the slab count must be the caller's
   const int kps = g.sps * DV_KS, splits = g.splits, cgroups = g.cgroups, mt = g.mt;
   if (a8) {
-    if (mt == 1) return launch_gemv<1, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
-    if (mt == 2) return launch_gemv<2, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
-    if (mt == 3) return launch_gemv<3, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
-    return launch_gemv<4, true, true>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    if (mt == 1) return launch_gemv<1, true, true, 1>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    if (mt == 2) return launch_gemv<2, true, true, 1>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    if (mt == 3) return launch_gemv<3, true, true, 1>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+    return launch_gemv<4, true, true, 1>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
   }
-  if (mt == 1) return launch_gemv<1, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
-  if (mt == 2) return launch_gemv<2, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
-  if (mt == 3) return launch_gemv<3, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
-  return launch_gemv<4, false, false>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+#define TQ_GEMV(MT_, NB_) \
+  if (mt == MT_ && g.nb == NB_) \
+    return launch_gemv<MT_, false, false, NB_>(a, b_col, C, M, N, K, kps, splits, cgroups, partials, st);
+  TQ_GEMV(1, 1)
+  TQ_GEMV(2, 1) TQ_GEMV(2, 2) TQ_GEMV(2, 4)
+  TQ_GEMV(3, 1) TQ_GEMV(3, 2) TQ_GEMV(3, 4)
+  TQ_GEMV(4, 1) TQ_GEMV(4, 2) TQ_GEMV(4, 4)
+#undef TQ_GEMV
+  return TQ_ERR_UNSUPPORTED;
 }
 
 }  // namespace
@@ -316,6 +352,12 @@ int run_gemv(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, in
 extern "C" int tq_int4_gemv_splitk(const uint8_t* a_pack, const int8_t* a_q8, const uint8_t* b_col, int32_t* C, int M,
                                    int N, int K, int split_k, void* stream) {
   return tq::run_gemv(a_pack, a_q8, b_col, C, M, N, K, split_k, false, (cudaStream_t)stream);
+}
+
+extern "C" int tq_set_gemv_channel_tiles(int tiles) {
+  if (tiles != -1 && tiles != 1 && tiles != 2 && tiles != 4) return TQ_ERR_BAD_ARG;
+  tq::g_gemv_tiles = tiles;
+  return TQ_OK;
 }
 
 extern "C" int tq_int4_gemv_plan(int M, int N, int K, int a_is_int8) {

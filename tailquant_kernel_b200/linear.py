@@ -172,7 +172,15 @@ class SplitLinear:
                                  rms_eps=float(h.get("rms_eps") or 1e-6))
 
     def _use_mma(self, M: int) -> bool:
-        return self.tail_engine == "mma" and M > self.small_m
+        # the fused prefill kernels also serve 48..64 rows of the wide projections: there the row-gather tail of the
+        # small-M path reads M R weight rows of 2 N bytes and takes longer than a whole 128-row tile (gate_up at 64
+        # rows: 137 us against 107 us)
+        return self.tail_engine == "mma" and (M > self.small_m or (M >= 48 and self.N >= 12288))
+
+    def _decode_uses_tc(self, M: int) -> bool:
+        # dense part of the small-M path: the weight-streaming GEMV, except beyond 48 rows on the widest projections,
+        # where the tcgen05 split-K GEMM (int32 atomics into one slab) is ahead (34 against 38 us on gate_up at 64)
+        return M > 48 and self.N >= 16384
 
     @property
     def N_out(self) -> int:
@@ -182,7 +190,7 @@ class SplitLinear:
         ws = self._ws.get(M)
         if ws is None:
             ws = self._ws[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M),
-                                          M <= self.small_m, self.N_out,
+                                          not self._use_mma(M) and M <= self.small_m, self.N_out,
                                           dense=self.w.had_kind == ops.TQ_HAD_BLOCK128)
         return ws
 
@@ -195,7 +203,8 @@ class SplitLinear:
         own = self._ws_shared.get(M)
         if own is None:
             own = self._ws_shared[M] = _Workspace(M, self.K, self.N, self.R, self.w.b_col.device, self._use_mma(M),
-                                                  M <= self.small_m, self.N_out, with_pro=False)
+                                                  not self._use_mma(M) and M <= self.small_m, self.N_out,
+                                                  with_pro=False)
         return own
 
     def _pick_split_k(self, M: int) -> int:
@@ -228,9 +237,7 @@ class SplitLinear:
             return ops.split_gemm_mma(pro.a_q8, pro.body_scale, w.b_col, w.w_scale, own.out, w_rot=w.w_rot, pro=pro,
                                       R=self.R, bias=w.bias, act=self.epilogue)
         if M <= self.small_m:  # decode: weight-streaming GEMV + row gather, both HBM-bound
-            # 32 rows and more on the wide projections: the tcgen05 split-K GEMM (int32 atomics into one slab) is
-            # ahead of the mma.sync GEMV there (measured 34 against 43 us at M = 64 on gate_up)
-            tc = M >= 32 and self.N >= 6144
+            tc = self._decode_uses_tc(M)
             if own.acc is None:  # partial sums per K range: one GEMV launch (no zeroing, no atomics) + the finisher
                 splits = 1 if tc else ops.gemv_plan(M, self.N, self.K)
                 own.acc = torch.empty((splits, M, self.N), dtype=torch.int32, device=own.out.device)

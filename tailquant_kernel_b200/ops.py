@@ -338,6 +338,12 @@ def set_gemm_pair_mode(mode: int) -> None:
     _lib.check(_lib.load().tq_set_gemm_pair_mode(int(mode)), "set_gemm_pair_mode")
 
 
+def set_gemv_channel_tiles(tiles: int) -> None:
+    """8-channel tiles per warp of the decode GEMV for calls with more than 16 rows: -1 (default: 4), 1, 2 or 4.
+    `gemv_plan` follows it, so buffers of partial sums sized before a change no longer fit."""
+    _lib.check(_lib.load().tq_set_gemv_channel_tiles(int(tiles)), "set_gemv_channel_tiles")
+
+
 def set_prologue_mode(mode: int) -> None:
     """-1: the prologue kernel specialised for K = 4096 / 12288 / 14336 where it applies; 0: the general kernel only
     (both give the same bits; a switch for comparisons)."""
