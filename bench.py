@@ -143,6 +143,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.power_w, self.capped = [], 0
         self._stop = threading.Event()
         self._t = None
         try:
@@ -172,6 +173,8 @@ class ClockSampler:
                 for bit, name in names.items():
                     if mask & bit:
                         self.reasons.add(name)
+                self.capped += 1 if mask & getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4) else 0
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
             except Exception:
                 pass
             time.sleep(0.002)
@@ -188,6 +191,11 @@ class ClockSampler:
         s = sorted(self.samples)
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
                 "samples": len(s)}
+
+    def power_summary(self):
+        p = sorted(self.power_w)
+        return {"power_w": p[len(p) // 2] if p else None,
+                "sw_power_cap_fraction": (self.capped / len(self.samples)) if self.samples else None}
 
 
 # --------------------------------------------------------------------------------------- GPU arm
@@ -394,6 +402,34 @@ def run_ours(args) -> None:
 
     graph_split_ms = graph_median_ms(step)
     graph_bf16_ms = graph_median_ms(step_bf16)
+
+    # ---- the same layer graphs replayed for about two seconds each: what the board sustains under its power cap
+    # (the timed region above is some tens of milliseconds at burst clocks)
+    def sustained(fn, burst_ms, seconds=2.0):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        n = max(50, int(seconds / (burst_ms * 1e-3)))
+        sampler = ClockSampler(local)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.start()
+        e0.record()
+        for _ in range(n):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        clk = sampler.stop()
+        out = {"layer_ms": e0.elapsed_time(e1) / n, "replays": n, "sm_mhz": clk["sm_mhz"]}
+        out.update(sampler.power_summary())
+        return out
+
+    sustained_split = sustained(step, graph_split_ms, args.sustained_seconds) if args.sustained_seconds > 0 else None
+    sustained_bf16 = sustained(step_bf16, graph_bf16_ms, args.sustained_seconds) if args.sustained_seconds > 0 else None
     del Wbs
 
     # ---- plain pinned copies of one step's inputs and outputs, no compute: the ceiling of the end-to-end figure
@@ -519,6 +555,11 @@ def run_ours(args) -> None:
         "bf16_cublas_linear_ms_per_step": bf16_ms,
         "int8_cublas_gemm_ms_per_step": int8_ms,
         "split_over_bf16": ms_step / bf16_ms,
+        "sustained": None if sustained_split is None else {
+            "split": sustained_split, "bf16_cublas": sustained_bf16,
+            "split_over_bf16": sustained_split["layer_ms"] / sustained_bf16["layer_ms"],
+            "tops": ops_step_of(M_TOKENS) / (sustained_split["layer_ms"] * 1e-3) / 1e12,
+            "protocol": "the layer's CUDA graph replayed for about 2 s; clocks and power are NVML medians over that time"},
         "graph_latency": {"split_layer_ms": graph_split_ms, "bf16_cublas_layer_ms": graph_bf16_ms,
                           "split_over_bf16": graph_split_ms / graph_bf16_ms,
                           "protocol": "one CUDA graph per layer (4 linears), 5 warm-ups, 30 replays, median of 5 runs"},
@@ -889,6 +930,8 @@ def main() -> None:
     global M_TOKENS, METRIC, CPU_SAMPLE_ROWS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="layer workload: also replay the layer graphs this long and report what the board sustains (0 = skip)")
     ap.add_argument("--rows-per-gpu", type=int, default=M_TOKENS,
                     help="token rows per GPU (2048 = the headline config; 4096 per GPU on 8 GPUs is the M = 32768 run)")
     ap.add_argument("--steps", type=int, default=50)
