@@ -304,10 +304,20 @@ GemvPlan plan_gemv(int M, int N, int K, int split_k, bool a8) {
   // groups of 64 channels per CTA (sharing the staged activations): more than one measured slower at every M
   // on the Qwen3-8B layer shapes -- the smaller grid costs more than the repeated staging
   g.cgroups = 1;
-  if (split_k < 1) {  // four CTAs per SM, eight for the wide projections (timed on the Qwen3-8B layer shapes)
+  if (split_k < 1) {
     const int ctas_n = (N + DV_CH * g.nb * g.cgroups - 1) / (DV_CH * g.nb * g.cgroups);
-    const int per_sm = g.nb == 1 ? (ctas_n >= 256 ? 8 : 4) : 2;
-    split_k = (per_sm * 148 + ctas_n - 1) / ctas_n;
+    if (g.nb == 1 && g.mt == 1) {
+      // Up to 16 rows: a K range of eight slices -- exactly the eight weight loads a lane keeps in flight, requested
+      // in one go before anything else happens in the CTA -- was the fastest split on every Qwen3-8B layer shape
+      // (weights from HBM: qkv 6.1 us with 4 ranges against 6.9 with 7, o 4.9 against 5.8 with 8, down 9.8 with 12
+      // against 11.0 with 10, gate_up 15.2 with 4); shorter ranges only where that leaves SMs without a CTA
+      int sps = slices < 8 ? slices : 8;
+      while (sps > 1 && (long)ctas_n * ((slices + sps - 1) / sps) < 148) --sps;
+      split_k = (slices + sps - 1) / sps;
+    } else {  // (timed likewise) four CTAs per SM with one channel tile per warp, two with four tiles
+      const int per_sm = g.nb == 1 ? (ctas_n >= 256 ? 8 : 4) : 2;
+      split_k = (per_sm * 148 + ctas_n - 1) / ctas_n;
+    }
   }
   if (split_k > slices) split_k = slices;
   g.sps = (slices + split_k - 1) / split_k;  // slices per split
