@@ -880,9 +880,13 @@ def test_gemv_partials_and_finisher(M, N, K):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("M,K,I,ratio,pair", [(300, 1024, 264, 0.05, 0), (300, 1024, 264, 0.05, 1), (257, 4096, 512, 0.0, 1),
-                                              (8, 4096, 512, 0.05, -1), (40, 1024, 136, 0.05, -1)])
-def test_swiglu_epilogue(M, K, I, ratio, pair):
+@pytest.mark.parametrize("M,K,I,ratio,pair,kind", [(300, 1024, 264, 0.05, 0, None), (300, 1024, 264, 0.05, 1, None),
+                                                   (257, 4096, 512, 0.0, 1, None), (8, 4096, 512, 0.05, -1, None),
+                                                   (40, 1024, 136, 0.05, -1, None),
+                                                   # block rotation: the zero-filled tail matrix (general prologue
+                                                   # kernel) feeds the pair kernel's long runs
+                                                   (300, 2048, 264, 0.10, 1, O.HAD_BLOCK128)])
+def test_swiglu_epilogue(M, K, I, ratio, pair, kind):
     """The fused gate_up layer with the SwiGLU epilogue equals SwiGLU (CPU oracle) applied to the same layer's
     plain bf16 outputs: the two runs share every kernel up to the epilogue, so only exp() may differ."""
     from tailquant_kernel_b200 import SplitLinear, interleave_gate_up
@@ -895,11 +899,14 @@ def test_swiglu_epilogue(M, K, I, ratio, pair):
     x = dev_bf16(O.make_activations(M, K, seed=5, n_outlier=8))
     ops.set_gemm_pair_mode(pair)
     try:
-        plain = SplitLinear(W, bias=bias, ratio=ratio)
-        fused = SplitLinear(W, bias=bias, ratio=ratio, epilogue="swiglu")
+        plain = SplitLinear(W, bias=bias, ratio=ratio, had_kind=kind)
+        fused = SplitLinear(W, bias=bias, ratio=ratio, epilogue="swiglu", had_kind=kind)
         y = host_bits(plain(x))
         h = fused(x)
         torch.cuda.synchronize()
+        if kind == O.HAD_BLOCK128:
+            pro = fused.workspace(M).pro
+            assert pro.tail_dense is not None and int((pro.tail_cnt > ops.TAIL_REC_CAP).sum()) > 0
     finally:
         ops.set_gemm_pair_mode(-1)
     assert tuple(h.shape) == (M, I)
