@@ -625,7 +625,9 @@ def run_extra(args) -> None:
     single      : baseline config 1 (M = 512, K = N = 4096, ratio 0.05), both tail engines
     latency_table : CSV `K,N,ratio,b16,b64,b256` (ms per forward at 16 / 64 / 256 token rows, CUDA-graph replay) in
                   the format the reference's policy calibrator reads
-                  (tools/calibrate_shape_latency_cegrad_ratio_v1.py:365-440), Qwen3-8B per-projection shapes"""
+                  (tools/calibrate_shape_latency_cegrad_ratio_v1.py:365-440), Qwen3-8B per-projection shapes
+    probe       : a few untimed launches of ONE kernel of ONE linear of the layer (`--only`, `--probe prologue|gemm`,
+                  `--ratio`, `--steps` launches at `--rows-per-gpu` rows): a small target for a profiler capture"""
     import torch
     from tailquant_kernel_b200 import SplitLinear
 
@@ -669,7 +671,24 @@ def run_extra(args) -> None:
         x[:, torch.randperm(K, generator=g)[: max(16, K // 100)]] *= 50.0
         return x.to(torch.bfloat16).to(dev), W
 
-    if args.workload == "decode":
+    if args.workload == "probe":
+        from tailquant_kernel_b200 import ops as _ops
+        from tailquant_kernel_b200._lib import TQ_HAD_KRON12, TQ_HAD_WHT
+        name, K, N = next((l for l in LAYER if l[0] == (args.only or "o_proj")))
+        M = args.rows_per_gpu
+        x, W = data(M, K, N, 7)
+        lin = SplitLinear(W, ratio=args.ratio, had_kind=TQ_HAD_KRON12 if K == 12288 else TQ_HAD_WHT)
+        del W
+        ws = lin.prologue(x)
+        for _ in range(max(1, args.steps)):
+            if args.probe == "prologue":
+                lin.prologue(x)
+            else:
+                lin.compute(ws, M)
+        torch.cuda.synchronize()
+        print(json.dumps({"workload": "probe", "linear": name, "M": M, "K": K, "N": N, "R": lin.R, "kernel": args.probe,
+                          "launches": max(1, args.steps)}), flush=True)
+    elif args.workload == "decode":
         for name, K, N in LAYER:
             if args.only and name != args.only:
                 continue
@@ -940,11 +959,14 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tail-engine", default="mma", choices=["mma", "gather"],
                     help="mma: tail on the tensor cores inside the GEMM kernel; gather: exact-order CUDA-core kernel")
-    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "llama_sweep", "single", "latency_table", "prefill36"],
+    ap.add_argument("--workload", default="layer",
+                    choices=["layer", "decode", "llama_sweep", "single", "latency_table", "prefill36", "probe"],
                     help="layer = the benchmark proper (baseline configs[1]); the others print secondary figures")
     ap.add_argument("--reference-rows", type=int, default=CPU_SAMPLE_ROWS,
                     help="token rows of the 2048 that the CPU arm (and the cpu_baseline leg) works through per step")
-    ap.add_argument("--only", default="", help="decode: restrict to one linear (qkv_proj, o_proj, gate_up_proj, down_proj)")
+    ap.add_argument("--only", default="", help="decode / probe: restrict to one linear (qkv_proj, o_proj, gate_up_proj, down_proj)")
+    ap.add_argument("--probe", default="gemm", choices=["prologue", "gemm"], help="probe: which kernel of the linear to launch")
+    ap.add_argument("--ratio", type=float, default=RATIO, help="probe: tail ratio (0 = pure W4A4)")
     ap.add_argument("--layers", type=int, default=36, help="prefill36: decoder layers")
     ap.add_argument("--seq-len", type=int, default=4096, help="prefill36: tokens")
     ap.add_argument("--with-bf16", action="store_true", help="prefill36: also time the same stack on bf16 cuBLAS linears")
