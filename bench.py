@@ -676,6 +676,7 @@ def run_extra(args) -> None:
         from tailquant_kernel_b200._lib import TQ_HAD_KRON12, TQ_HAD_WHT
         name, K, N = next((l for l in LAYER if l[0] == (args.only or "o_proj")))
         M = args.rows_per_gpu
+        _ops.set_prologue_mode(args.prologue_mode)
         x, W = data(M, K, N, 7)
         lin = SplitLinear(W, ratio=args.ratio, had_kind=TQ_HAD_KRON12 if K == 12288 else TQ_HAD_WHT)
         del W
@@ -967,6 +968,8 @@ def main() -> None:
     ap.add_argument("--only", default="", help="decode / probe: restrict to one linear (qkv_proj, o_proj, gate_up_proj, down_proj)")
     ap.add_argument("--probe", default="gemm", choices=["prologue", "gemm"], help="probe: which kernel of the linear to launch")
     ap.add_argument("--ratio", type=float, default=RATIO, help="probe: tail ratio (0 = pure W4A4)")
+    ap.add_argument("--prologue-mode", type=int, default=-1, choices=[-1, 0],
+                    help="probe: 0 = the general prologue kernel also where the specialised one is built")
     ap.add_argument("--layers", type=int, default=36, help="prefill36: decoder layers")
     ap.add_argument("--seq-len", type=int, default=4096, help="prefill36: tokens")
     ap.add_argument("--with-bf16", action="store_true", help="prefill36: also time the same stack on bf16 cuBLAS linears")
